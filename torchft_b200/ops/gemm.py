@@ -1,0 +1,55 @@
+"""bf16 GEMM on the 5th-generation tensor cores (``csrc/kernels/gemm_tcgen05.cu``)."""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    out: Optional[torch.Tensor] = None,
+    *,
+    a_kmajor: bool = True,
+    b_kmajor: bool = True,
+    accumulate: bool = False,
+    out_dtype: torch.dtype = torch.bfloat16,
+    status: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``out (+)= op(a) @ op(b)`` with fp32 accumulation.
+
+    ``a_kmajor``: ``a`` is stored ``[M, K]``; otherwise ``[K, M]`` (used as ``a.T``).
+    ``b_kmajor``: ``b`` is stored ``[N, K]`` (used as ``b.T``, the ``nn.Linear`` weight
+    layout); otherwise ``[K, N]``.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_kmajor:
+        M, K = a.shape
+    else:
+        K, M = a.shape
+    if b_kmajor:
+        N, Kb = b.shape
+    else:
+        Kb, N = b.shape
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    code = _lib.lib().tft_gemm_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(0 if a_kmajor else 1), ctypes.c_int(0 if b_kmajor else 1),
+        ctypes.c_int(1 if out.dtype == torch.float32 else 0), ctypes.c_int(1 if accumulate else 0),
+        _lib.ptr(status), _lib.stream_ptr(),
+    )
+    _lib.check(code, "tft_gemm_bf16")
+    _lib.count_launch()
+    return out
