@@ -1,0 +1,209 @@
+"""Table tests of the pure quorum rules (C++: csrc/control/quorum.cc).
+
+Scenarios follow the reference's unit tests in src/lighthouse.rs:584-1037 and
+src/manager.rs:720-850.
+"""
+
+import pytest
+
+from torchft_b200 import _control as C
+
+
+def member(rid, step=1, shrink_only=False, addr=None):
+    return {
+        "replica_id": rid,
+        "address": addr or f"addr_{rid}",
+        "store_address": f"store_{rid}",
+        "step": step,
+        "world_size": 1,
+        "shrink_only": shrink_only,
+    }
+
+
+def part(rid, joined, **kw):
+    return {"joined": joined, "member": member(rid, **kw)}
+
+
+def test_join_timeout_waits_for_stragglers():
+    now = 100.0
+    state = {"participants": {}, "heartbeats": {}, "prev_quorum": None}
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=60000)
+    assert members is None
+    assert "New quorum not ready, only have 0 participants, need min_replicas 1" in reason
+
+    state["participants"]["a"] = part("a", now)
+    state["heartbeats"]["a"] = now
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=60000)
+    assert members is not None and [m["replica_id"] for m in members] == ["a"]
+    assert "Valid quorum found" in reason
+
+    # c heartbeats but has not asked yet: wait for it until the join timeout passes
+    state["participants"]["b"] = part("b", now)
+    state["heartbeats"]["b"] = now
+    state["heartbeats"]["c"] = now
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=60000)
+    assert members is None
+    assert "Valid quorum with 2 participants, waiting for 1 healthy but not participating stragglers due to join timeout" in reason
+
+    members, reason = C.quorum_compute(now + 61.0, state, min_replicas=1, join_timeout_ms=60000, heartbeat_timeout_ms=10**9)
+    assert members is not None and len(members) == 2
+    assert "Valid quorum found" in reason
+
+
+def test_heartbeat_expiry_drops_participant():
+    now = 100.0
+    state = {
+        "participants": {"a": part("a", now), "b": part("b", now)},
+        "heartbeats": {"a": now, "b": now - 10.0},  # b stopped 10 s ago (timeout 5 s)
+        "prev_quorum": None,
+    }
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=0)
+    assert [m["replica_id"] for m in members] == ["a"]
+    assert "[1/2 participants healthy][1 heartbeating]" in reason
+
+
+def test_min_replicas():
+    now = 5.0
+    state = {"participants": {"a": part("a", now)}, "heartbeats": {"a": now}, "prev_quorum": None}
+    members, reason = C.quorum_compute(now, state, min_replicas=2, join_timeout_ms=0)
+    assert members is None
+    assert "New quorum not ready, only have 1 participants, need min_replicas 2" in reason
+
+
+def test_fast_quorum_and_expansion():
+    now = 50.0
+    prev = {"quorum_id": 1, "participants": [member("a"), member("b")]}
+    state = {
+        "participants": {"a": part("a", now), "b": part("b", now)},
+        "heartbeats": {"a": now, "b": now},
+        "prev_quorum": prev,
+    }
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=60000)
+    assert "Fast quorum found!" in reason
+    assert [m["replica_id"] for m in members] == ["a", "b"]
+
+    # a newcomer is admitted by the fast path without waiting
+    state["participants"]["c"] = part("c", now)
+    state["heartbeats"]["c"] = now
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=60000)
+    assert "Fast quorum found!" in reason
+    assert [m["replica_id"] for m in members] == ["a", "b", "c"]
+
+    # a previous member is missing: no fast path, b still heartbeats without asking
+    del state["participants"]["b"]
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=60000)
+    assert members is None
+    assert "waiting for 1 healthy but not participating stragglers" in reason
+
+
+def test_shrink_only_keeps_previous_members():
+    now = 7.0
+    prev = {"quorum_id": 3, "participants": [member("a"), member("b")]}
+    state = {
+        "participants": {
+            "a": part("a", now, shrink_only=True),
+            "b": part("b", now),
+            "c": part("c", now),
+        },
+        "heartbeats": {"a": now, "b": now, "c": now},
+        "prev_quorum": prev,
+    }
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=0)
+    assert [m["replica_id"] for m in members] == ["a", "b"]
+    assert "[shrink_only=true]" in reason
+
+
+def test_split_brain_needs_majority_of_heartbeating():
+    now = 9.0
+    state = {
+        "participants": {"a": part("a", now)},
+        "heartbeats": {"a": now, "b": now, "c": now},
+        "prev_quorum": None,
+    }
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=0)
+    assert members is None
+    assert "New quorum not ready, only have 1 participants, need at least half of 3 healthy workers" in reason
+
+    state["participants"]["b"] = part("b", now)
+    members, reason = C.quorum_compute(now, state, min_replicas=1, join_timeout_ms=0)
+    assert members is not None and len(members) == 2
+
+
+def test_quorum_changed_only_looks_at_replica_ids():
+    a = [member("a", step=1), member("b", step=1)]
+    b = [member("a", step=5, addr="other"), member("b", step=7)]
+    assert not C.quorum_changed(a, b)
+    assert C.quorum_changed(a, [member("a"), member("c")])
+    assert C.quorum_changed(a, [member("a")])
+
+
+def test_results_first_step_everyone_heals_from_primary():
+    members = [member("replica_0", step=0), member("replica_1", step=0)]
+    r0 = C.compute_quorum_results("replica_0", 0, 1, members)
+    assert not r0.heal
+    assert r0.replica_rank == 0 and r0.replica_world_size == 2
+    assert r0.recover_src_rank is None
+    assert r0.recover_dst_ranks == [1]
+    assert r0.max_step == 0 and r0.max_rank == 0 and r0.max_world_size == 2
+    assert r0.store_address == "store_replica_0"
+
+    r1 = C.compute_quorum_results("replica_1", 0, 1, members)
+    assert r1.heal
+    assert r1.recover_src_rank == 0
+    assert r1.recover_src_manager_address == "addr_replica_0"
+    assert r1.recover_dst_ranks == []
+    assert r1.max_rank == 1
+
+    # local rank 1 uses the second member as primary
+    r = C.compute_quorum_results("replica_0", 1, 1, members)
+    assert r.heal and r.recover_src_rank == 1 and r.store_address == "store_replica_1"
+    r = C.compute_quorum_results("replica_1", 1, 1, members)
+    assert not r.heal and r.recover_dst_ranks == [0]
+
+
+def test_results_recovery_round_robin():
+    steps = [0, 1, 0, 1, 0]
+    members = [member(f"replica_{i}", step=s) for i, s in enumerate(steps)]
+    r = C.compute_quorum_results("replica_0", 0, 1, members)
+    assert r.heal and r.recover_src_rank == 1 and r.max_rank is None and r.max_world_size == 2
+    assert r.max_step == 1 and r.replica_rank == 0 and r.replica_world_size == 5
+    assert r.store_address == "store_replica_1"
+
+    r = C.compute_quorum_results("replica_1", 0, 1, members)
+    assert not r.heal and r.recover_dst_ranks == [0, 4] and r.max_rank == 0
+    r = C.compute_quorum_results("replica_3", 0, 1, members)
+    assert not r.heal and r.recover_dst_ranks == [2] and r.max_rank == 1
+
+    # local rank 1 shifts the assignment and the primary store
+    r = C.compute_quorum_results("replica_1", 1, 1, members)
+    assert r.recover_dst_ranks == [2]
+    assert r.store_address == "store_replica_3"
+    r = C.compute_quorum_results("replica_3", 1, 1, members)
+    assert r.recover_dst_ranks == [0, 4]
+
+
+def test_results_unknown_replica():
+    with pytest.raises(RuntimeError, match="not participating in returned quorum"):
+        C.compute_quorum_results("nope", 0, 1, [member("a")])
+
+
+def test_parse_grpc_timeout():
+    assert C.parse_grpc_timeout("1H") == 3600.0
+    assert C.parse_grpc_timeout("2M") == 120.0
+    assert C.parse_grpc_timeout("3S") == 3.0
+    assert C.parse_grpc_timeout("250m") == 0.25
+    assert abs(C.parse_grpc_timeout("5u") - 5e-6) < 1e-12
+    assert abs(C.parse_grpc_timeout("7n") - 7e-9) < 1e-15
+    assert C.parse_grpc_timeout("") is None
+    assert C.parse_grpc_timeout("12") is None
+    assert C.parse_grpc_timeout("x5S") is None
+    assert C.parse_grpc_timeout("123456789S") is None  # more than 8 digits
+
+
+def test_retry_backoff():
+    ok, attempts = C.retry_backoff_probe(fail_times=3, initial_ms=1)
+    assert ok and attempts == 4
+    ok, attempts = C.retry_backoff_probe(fail_times=100, initial_ms=1, max_retries=2)
+    assert not ok and attempts == 3
+    ok, attempts = C.retry_backoff_probe(fail_times=10**6, initial_ms=5, timeout_ms=50)
+    assert not ok and attempts >= 2

@@ -108,8 +108,11 @@ def build_control(force: bool = False) -> Path:
     headers = sorted(CONTROL_SRC.glob("*.h"))
     out = control_module_path()
     newest = max(_newest(sources), _newest(headers))
-    cxx = os.environ.get("CXX", "g++")
-    common = ["-O2", "-std=c++17", "-fPIC", "-pthread", "-Wall", "-Wno-unused-function"]
+    # Prefer the distribution compiler: it links libstdc++ dynamically, so the module
+    # shares one C++ runtime with torch.  -Bsymbolic keeps a statically linked runtime
+    # (other toolchains) from being half-interposed by the process-wide one.
+    cxx = os.environ.get("TFT_CXX") or ("/usr/bin/g++" if Path("/usr/bin/g++").exists() else os.environ.get("CXX", "g++"))
+    common = ["-O2", "-std=c++17", "-fPIC", "-pthread", "-Wall", "-Wno-unused-function", "-Wl,-Bsymbolic"]
     if force or not out.exists() or out.stat().st_mtime < newest:
         py_inc = sysconfig.get_paths()["include"]
         cmd = [cxx, *common, "-shared", "-fvisibility=hidden", "-I", pybind11.get_include(), "-I", py_inc,
