@@ -20,6 +20,9 @@ def pytest_configure(config):
         build.build_control()
     if not build.kernels_lib_path().exists():
         build.build_kernels()
+    from torchft_b200 import _control
+
+    _control.set_log_enabled(False)
 
 
 def pytest_collection_modifyitems(config, items):

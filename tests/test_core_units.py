@@ -1,0 +1,191 @@
+"""Unit tests of futures, checkpoint transport, optimizer wrapper, sampler, DDP hook.
+
+Scenarios follow the reference's futures_test.py, checkpointing_test.py, optim_test.py,
+data_test.py and ddp_test.py.
+"""
+
+import threading
+import time
+import urllib.error
+from datetime import timedelta
+from unittest.mock import MagicMock, create_autospec
+
+import pytest
+import torch
+import torch.distributed as dist
+from torch import nn
+from torch.futures import Future
+
+from torchft_b200.checkpointing import CheckpointServer, _timed_acquire
+from torchft_b200.data import DistributedSampler
+from torchft_b200.ddp import DistributedDataParallel, PureDistributedDataParallel
+from torchft_b200.futures import future_timeout, future_wait
+from torchft_b200.manager import Manager
+from torchft_b200.optim import OptimizerWrapper
+
+
+# ------------------------------------------------------------------ futures
+def test_future_wait_result_and_timeout():
+    fut = Future()
+    with pytest.raises(TimeoutError, match="future did not complete within"):
+        future_wait(fut, timedelta(seconds=0.01))
+    fut = Future()
+    fut.set_result(1)
+    assert future_wait(fut, timedelta(seconds=1.0)) == 1
+    fut = Future()
+    fut.set_exception(RuntimeError("test"))
+    with pytest.raises(RuntimeError, match="test"):
+        future_wait(fut, timedelta(seconds=1.0))
+
+
+def test_future_timeout_fires():
+    fut = Future()
+    timed = future_timeout(fut, timedelta(seconds=0.01))
+    with pytest.raises(TimeoutError, match="future did not complete within"):
+        timed.wait()
+
+
+def test_future_timeout_passes_result_and_exception():
+    fut = Future()
+    timed = future_timeout(fut, timedelta(seconds=10))
+    fut.set_result(5)
+    assert timed.wait() == 5
+    fut = Future()
+    timed = future_timeout(fut, timedelta(seconds=10))
+    fut.set_exception(RuntimeError("boom"))
+    with pytest.raises(RuntimeError, match="boom"):
+        timed.wait()
+
+
+def test_future_timeout_many_deadlines_in_order():
+    futs = [Future() for _ in range(20)]
+    timed = [future_timeout(f, timedelta(seconds=0.02 + 0.001 * i)) for i, f in enumerate(futs)]
+    futs[3].set_result("ok")
+    assert timed[3].wait() == "ok"
+    for i, t in enumerate(timed):
+        if i == 3:
+            continue
+        with pytest.raises(TimeoutError):
+            t.wait()
+
+
+# ------------------------------------------------------------------ checkpoint server
+def test_checkpoint_server_round_trip_and_gate():
+    expected = {"state": "dict", "tensor": torch.arange(5)}
+    server = CheckpointServer(timeout=timedelta(seconds=10))
+    try:
+        server.send_checkpoint(dst_ranks=[], step=1234, state_dict=expected, timeout=timedelta(seconds=10))
+        meta = server.metadata()
+        assert meta.endswith("/checkpoint/")
+        out = server.recv_checkpoint(src_rank=0, metadata=meta, step=1234, timeout=timedelta(seconds=10))
+        assert out["state"] == "dict" and torch.equal(out["tensor"], expected["tensor"])
+
+        # wrong step -> 400
+        with pytest.raises(urllib.error.HTTPError, match="Error 400"):
+            server.recv_checkpoint(src_rank=0, metadata=meta, step=1, timeout=timedelta(seconds=10))
+
+        # closed gate -> the request blocks until the (short) client timeout
+        server.disallow_checkpoint()
+        with pytest.raises((TimeoutError, urllib.error.URLError, OSError)):
+            server.recv_checkpoint(src_rank=0, metadata=meta, step=1234, timeout=timedelta(seconds=0.2))
+    finally:
+        server.shutdown()
+
+
+def test_checkpoint_server_gate_blocks_until_allowed():
+    server = CheckpointServer(timeout=timedelta(seconds=10))
+    try:
+        result = {}
+
+        def fetch():
+            result["v"] = server.recv_checkpoint(0, server.metadata(), 7, timedelta(seconds=10))
+
+        t = threading.Thread(target=fetch)
+        t.start()
+        time.sleep(0.2)
+        assert "v" not in result  # still gated
+        server.send_checkpoint([1], 7, {"x": 1}, timedelta(seconds=10))
+        t.join(timeout=10)
+        assert result["v"] == {"x": 1}
+    finally:
+        server.shutdown()
+
+
+def test_timed_acquire():
+    lock = threading.Lock()
+    with _timed_acquire(lock, timedelta(seconds=1)):
+        assert lock.locked()
+        with pytest.raises(TimeoutError, match="timed out acquiring lock after"):
+            with _timed_acquire(lock, timedelta(seconds=0.01)):
+                pass
+    assert not lock.locked()
+
+
+# ------------------------------------------------------------------ optimizer wrapper
+def test_optimizer_wrapper_gates_step():
+    manager = create_autospec(Manager)
+    m = nn.Linear(3, 4)
+    base = torch.optim.AdamW(m.parameters())
+    optim = OptimizerWrapper(manager, base)
+    optim.add_param_group({"params": nn.Linear(2, 2).parameters(), "lr": 1})
+    assert len(optim.param_groups) == 2
+    optim.load_state_dict(optim.state_dict())
+
+    optim.zero_grad()
+    assert manager.start_quorum.call_count == 1
+
+    m(torch.rand(2, 3)).sum().backward()
+    before = [p.detach().clone() for p in m.parameters()]
+    manager.should_commit.return_value = False
+    optim.step()
+    assert all(torch.equal(a, b) for a, b in zip(before, m.parameters()))
+    manager.should_commit.return_value = True
+    optim.step()
+    assert manager.should_commit.call_count == 2
+    assert not all(torch.equal(a, b) for a, b in zip(before, m.parameters()))
+    assert optim.state is base.state
+
+
+# ------------------------------------------------------------------ sampler
+def test_distributed_sampler_arithmetic():
+    dataset = list(range(1000))
+    sampler = DistributedSampler(dataset, replica_group=1, num_replica_groups=2, rank=3, num_replicas=4, shuffle=False)
+    assert sampler.global_rank == 3 + 1 * 4
+    assert sampler.global_world_size == 8
+    it = iter(sampler)
+    assert next(it) == 7
+    assert next(it) == 15
+    assert len(sampler) == 125
+
+
+# ------------------------------------------------------------------ DDP
+def _manager_mock_allreduce():
+    manager = create_autospec(Manager)
+    calls = []
+
+    def allreduce(t):
+        calls.append(t.numel())
+        f = Future()
+        f.set_result(t)
+        return f
+
+    manager.allreduce = allreduce
+    return manager, calls
+
+
+def test_ddp_routes_buckets_through_manager():
+    manager, calls = _manager_mock_allreduce()
+    m = nn.Linear(3, 4)
+    ddp = DistributedDataParallel(manager, m)
+    ddp(torch.rand(2, 3)).mean().backward()
+    assert sum(calls) == sum(p.numel() for p in m.parameters())
+    for p in m.parameters():
+        assert p.grad is not None
+
+
+def test_pure_ddp_hooks_every_parameter():
+    manager, calls = _manager_mock_allreduce()
+    m = nn.Linear(3, 4)
+    ddp = PureDistributedDataParallel(manager, m)
+    ddp(torch.rand(2, 3)).mean().backward()
+    assert sorted(calls) == sorted(p.numel() for p in m.parameters())

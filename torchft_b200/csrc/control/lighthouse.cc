@@ -163,7 +163,7 @@ net::Status Lighthouse::handle_quorum(const net::CallContext& ctx, const std::st
   const wire::QuorumMember& requester = request.requester;
   if (requester.replica_id.empty())
     return net::Status::Error(net::kInvalidArgument, "missing requester");
-  net::log_info("torchft_b200::lighthouse", "got quorum request for replica " + requester.replica_id);
+  net::log_debug("torchft_b200::lighthouse", "got quorum request for replica " + requester.replica_id);
 
   std::unique_lock<std::mutex> lk(mu_);
   auto join = [&] {

@@ -125,7 +125,7 @@ net::Status ManagerServer::handle_quorum(const net::CallContext& ctx, const std:
   const net::Millis timeout = std::chrono::duration_cast<net::Millis>(*ctx.timeout);
   wire::ManagerQuorumRequest request = wire::ManagerQuorumRequest::decode(req);
   const int64_t rank = request.rank;
-  net::log_info("torchft_b200::manager",
+  net::log_debug("torchft_b200::manager",
                 "[Replica " + replica_id_ + "] Start quorum for rank " + std::to_string(rank));
 
   std::unique_lock<std::mutex> lk(mu_);
@@ -213,7 +213,7 @@ net::Status ManagerServer::handle_should_commit(const net::CallContext& ctx, con
   const uint64_t my_seq = commit_seq_;
   if (commit_votes_.size() >= world_size_) {
     last_commit_decision_ = commit_failures_.empty();
-    net::log_info("torchft_b200::manager", "[Replica " + replica_id_ + "] should_commit completed should_commit=" +
+    net::log_debug("torchft_b200::manager", "[Replica " + replica_id_ + "] should_commit completed should_commit=" +
                                                (last_commit_decision_ ? "true" : "false"));
     commit_votes_.clear();
     commit_failures_.clear();

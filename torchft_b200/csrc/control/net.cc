@@ -121,6 +121,14 @@ void log_info(const std::string& module, const std::string& msg) {
   (void)ignored;
 }
 
+void log_debug(const std::string& module, const std::string& msg) {
+  static const bool enabled = [] {
+    const char* v = std::getenv("TORCHFT_B200_LOG");
+    return v && std::string(v) == "debug";
+  }();
+  if (enabled) log_info(module, msg);
+}
+
 const char* code_name(int code) {
   switch (code) {
     case kOk: return "Ok";

@@ -160,6 +160,8 @@ class Client {
 };
 
 void log_info(const std::string& module, const std::string& msg);
+// Per-request chatter; printed only when TORCHFT_B200_LOG=debug.
+void log_debug(const std::string& module, const std::string& msg);
 void set_log_enabled(bool enabled);
 
 }  // namespace net

@@ -6,17 +6,11 @@ errors recorded instead of raised).  ``PureDistributedDataParallel`` is the hook
 variant without buckets.  Parity: the reference's ``torchft/ddp.py:32-97``.
 """
 
-from __future__ import annotations
-
-import os
-import sys
-from typing import TYPE_CHECKING, Optional
-from unittest.mock import patch
+from typing import TYPE_CHECKING
 
 import torch
-import torch.distributed.algorithms.ddp_comm_hooks.default_hooks as default
+import torch.distributed as dist
 from torch import nn
-from torch.distributed import ProcessGroup as BaseProcessGroup
 from torch.nn import parallel
 
 from torchft_b200.process_group import ProcessGroupDummy
@@ -46,7 +40,7 @@ class DistributedDataParallel(parallel.DistributedDataParallel):
         self.register_comm_hook(manager, self._comm_hook)
 
     @staticmethod
-    def _comm_hook(state: "Manager", bucket: "torch.distributed.GradBucket") -> "torch.futures.Future[torch.Tensor]":
+    def _comm_hook(state: "Manager", bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
         return state.allreduce(bucket.buffer())
 
 
