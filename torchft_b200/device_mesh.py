@@ -60,8 +60,10 @@ class ManagedDeviceMesh(DeviceMesh):
         # for the virtual dimension.
         if mesh is None and parent is None:
             raise ValueError("ManagedDeviceMesh doesn't support both mesh and parent are None.")
-        self.mesh = mesh
-        self.mesh_dim_names = mesh_dim_names
+        # DeviceMesh exposes mesh / mesh_dim_names / device_type as read-only properties;
+        # they are overridden below and backed by these private fields.
+        self._inner_mesh = mesh
+        self._dim_names = tuple(mesh_dim_names)
         self.replicate_pg = replicate_pg
         self.replicate_dim = replicate_dim
         self.replicate_dim_name: str = mesh_dim_names[replicate_dim]
@@ -69,9 +71,22 @@ class ManagedDeviceMesh(DeviceMesh):
         self.flatten_meshes: Dict[str, DeviceMesh] = {}
         inner = mesh if mesh is not None else parent
         assert inner is not None
-        self.device_type: str = inner.device_type
+        self._device_type: str = inner.device_type
         self._flatten_mesh_list: Tuple[DeviceMesh, ...] = tuple()
         self._thread_id: Optional[int] = None
+
+    @property
+    def mesh(self) -> Optional[DeviceMesh]:  # type: ignore[override]
+        """The real mesh of the dimensions inside the replica group (None for a replicate-only view)."""
+        return self._inner_mesh
+
+    @property
+    def mesh_dim_names(self) -> Tuple[str, ...]:  # type: ignore[override]
+        return self._dim_names
+
+    @property
+    def device_type(self) -> str:  # type: ignore[override]
+        return self._device_type
 
     # -- pickling
     def __getstate__(self) -> Dict[str, Any]:
