@@ -293,19 +293,20 @@ TFT_API int tft_gemm_bf16(const void* a, const void* b, void* c, int M, int N, i
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) ||
       (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
       (reinterpret_cast<uintptr_t>(c) & 15))
-    return static_cast<int>(cudaErrorInvalidValue);
+    return -1;  // misaligned pointer or leading dimension
   CUtensorMap ta, tb;
   bool ok;
   if (!a_mn)
     ok = make_tensormap(&ta, a, 2, 2, K, M, 1, uint64_t(lda) * 2, 0, BK, BM, 1, 1);
   else
     ok = make_tensormap(&ta, a, 2, 2, M, K, 1, uint64_t(lda) * 2, 0, 64, BK, 1, 1);
-  if (!ok) return static_cast<int>(cudaErrorInvalidValue);
+  if (!ok) return -2;  // tensor map of A rejected
   if (!b_mn)
     ok = make_tensormap(&tb, b, 2, 2, K, N, 1, uint64_t(ldb) * 2, 0, BK, BN, 1, 1);
   else
     ok = make_tensormap(&tb, b, 2, 2, N, K, 1, uint64_t(ldb) * 2, 0, 64, BK, 1, 1);
-  if (!ok) return static_cast<int>(cudaErrorInvalidValue);
+  if (!ok) return -3;  // tensor map of B rejected
+  cudaGetLastError();  // drop stale errors left by other libraries on this thread
 
   cudaError_t e;
 #define TFT_GEMM_DISPATCH(AM, BM_)                                                             \

@@ -7,6 +7,7 @@
 #include <cudaTypedefs.h>
 #include <stdint.h>
 
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -64,11 +65,22 @@ inline bool make_tensormap(CUtensorMap* out, const void* ptr, int rank, uint32_t
   CUtensorMapDataType dt = esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                          : esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                       : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  // The encoder is a driver call and needs a current context.  Threads that only ever
+  // used the runtime API lazily (autograd worker threads, for one) may not have bound the
+  // primary context yet; a no-op runtime call binds it.
+  cudaFree(nullptr);
   CUresult r = fn(out, dt, rank, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return false;
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr,
+                 "torchft_b200: cuTensorMapEncodeTiled failed (%d): ptr=%p rank=%d esize=%u dims=(%llu,%llu,%llu) "
+                 "strides=(%llu,%llu) box=(%u,%u,%u)\n",
+                 static_cast<int>(r), ptr, rank, esize, (unsigned long long)d0, (unsigned long long)d1,
+                 (unsigned long long)d2, (unsigned long long)s1, (unsigned long long)s2, b0, b1, b2);
+    return false;
+  }
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);

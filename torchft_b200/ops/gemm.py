@@ -42,13 +42,12 @@ def gemm(
         assert not accumulate
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     assert out.shape == (M, N) and out.stride(1) == 1
+    if status is None:
+        status = _lib.status_word(a.device)
     code = _lib.lib().tft_gemm_bf16(
-        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out),
-        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
-        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
-        ctypes.c_int(0 if a_kmajor else 1), ctypes.c_int(0 if b_kmajor else 1),
-        ctypes.c_int(1 if out.dtype == torch.float32 else 0), ctypes.c_int(1 if accumulate else 0),
-        _lib.ptr(status), _lib.stream_ptr(),
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        0 if a_kmajor else 1, 0 if b_kmajor else 1, 1 if out.dtype == torch.float32 else 0,
+        1 if accumulate else 0, _lib.ptr(status), _lib.stream_ptr(),
     )
     _lib.check(code, "tft_gemm_bf16")
     _lib.count_launch()
