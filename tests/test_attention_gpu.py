@@ -1,0 +1,67 @@
+"""Flash-attention kernels (tcgen05) against an fp32 PyTorch reference."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def reference(q, k, v, do):
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    qh = qf.permute(0, 2, 1, 3)
+    kh = kf.permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
+    vh = vf.permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
+    s = qh @ kh.transpose(-1, -2) / math.sqrt(D)
+    mask = torch.ones(S, S, device=q.device, dtype=torch.bool).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    o = (s.softmax(-1) @ vh).permute(0, 2, 1, 3)
+    o.backward(do.float())
+    return o.detach(), torch.logsumexp(s, -1).detach(), qf.grad, kf.grad, vf.grad
+
+
+def rel(a, b):
+    return ((a.float() - b).abs().max() / b.abs().max()).item()
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 1, 1, 128), (2, 512, 4, 2, 128), (1, 384, 4, 1, 64), (1, 200, 2, 2, 128), (1, 1024, 8, 2, 128)])
+def test_attention_fwd_bwd(shape):
+    from torchft_b200.ops import _lib
+    from torchft_b200.ops.attention import attention
+
+    B, S, Hq, Hkv, D = shape
+    torch.manual_seed(1)
+    q, k, v = (torch.randn(B, S, h, D, device="cuda").to(torch.bfloat16).requires_grad_() for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+    o = attention(q, k, v)
+    o.backward(do)
+    ro, _, rq, rk, rv = reference(q.detach(), k.detach(), v.detach(), do)
+    assert rel(o, ro) < 2e-2
+    assert rel(q.grad, rq) < 2e-2 and rel(k.grad, rk) < 2e-2 and rel(v.grad, rv) < 2e-2
+    _lib.check_status("attention")
+
+
+def test_attention_on_fused_qkv_views():
+    from torchft_b200.ops.attention import attention_bwd, attention_fwd
+
+    B, S, Hq, Hkv, D = 1, 512, 8, 2, 128
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    q = qkv[..., : Hq * D].view(B, S, Hq, D)
+    k = qkv[..., Hq * D : (Hq + Hkv) * D].view(B, S, Hkv, D)
+    v = qkv[..., (Hq + Hkv) * D :].view(B, S, Hkv, D)
+    do = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+    o, lse = attention_fwd(q, k, v)
+    dqkv = torch.zeros_like(qkv)
+    outs = (
+        dqkv[..., : Hq * D].view(B, S, Hq, D),
+        dqkv[..., Hq * D : (Hq + Hkv) * D].view(B, S, Hkv, D),
+        dqkv[..., (Hq + Hkv) * D :].view(B, S, Hkv, D),
+    )
+    attention_bwd(do, q, k, v, o, lse, out=outs)
+    ro, rl, rq, rk, rv = reference(q, k, v, do)
+    assert rel(o, ro) < 2e-2
+    assert (lse * math.log(2) - rl).abs().max().item() < 1e-3
+    assert rel(outs[0], rq) < 2e-2 and rel(outs[1], rk) < 2e-2 and rel(outs[2], rv) < 2e-2

@@ -1,0 +1,446 @@
+// Causal grouped-query flash attention, backward, on tcgen05 tensor cores.
+//
+// Three kernels:
+//   attn_delta_kernel   delta[row] = sum_d O[row,d] * dO[row,d]
+//   attn_dkdv_kernel    one CTA per (key tile, kv head): loops over the query heads of the
+//                       group and the query tiles at or after the key tile; dK and dV stay
+//                       in tensor memory for the whole loop (no atomics, deterministic)
+//   attn_dq_kernel      one CTA per (query tile, head): loops over key tiles, dQ stays in
+//                       tensor memory
+//
+// Per tile pair both kernels recompute S = Q K^T and dP = dO V^T with tcgen05.mma into
+// tensor memory; the softmax threads (one per query row) form P = exp2(S*c - LSE) and
+// dS = P * (dP - delta) and write them as bf16 into swizzled shared memory, from where
+// they feed the gradient MMAs as MN-major (transposed) or K-major operands.
+#include "attention_common.cuh"
+
+namespace tft {
+namespace attn {
+
+// ------------------------------------------------------------------ delta
+template <int HD>
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                  float* __restrict__ delta, int B, int S, int Hq) {
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * Hq;
+  if (gw >= total) return;
+  const int h = static_cast<int>(gw % Hq);
+  const long long tok = gw / Hq;
+  const int s = static_cast<int>(tok % S);
+  const int b = static_cast<int>(tok / S);
+  const __nv_bfloat16* o = O + (tok * Hq + h) * HD;
+  const __nv_bfloat16* d = dO + (tok * Hq + h) * HD;
+  float acc = 0.f;
+  for (int i = lane * 2; i < HD; i += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    acc += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<long long>(b) * Hq + h) * S + s] = acc;
+}
+
+// Writes 32 consecutive values of row r (columns c*32 .. c*32+31) as bf16 into a swizzled tile.
+__device__ __forceinline__ void store_row_chunk(uint8_t* tile, int r, int c, const float (&v)[32]) {
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    uint4 u;
+    u.x = pack_bf16(v[t * 8 + 0], v[t * 8 + 1]);
+    u.y = pack_bf16(v[t * 8 + 2], v[t * 8 + 3]);
+    u.z = pack_bf16(v[t * 8 + 4], v[t * 8 + 5]);
+    u.w = pack_bf16(v[t * 8 + 6], v[t * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + swizzled_chunk(r, c * 4 + t)) = u;
+  }
+}
+
+// Drains a [128 x HD] fp32 accumulator from tensor memory into global bf16 rows.
+template <int HD>
+__device__ __forceinline__ void store_acc(uint32_t taddr, __nv_bfloat16* dst, float mul, bool valid) {
+#pragma unroll 1
+  for (int c = 0; c < HD / 32; ++c) {
+    uint32_t a[32];
+    tmem_ld_32x32(taddr + c * 32, a);
+    tmem_ld_wait();
+    if (valid) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        uint4 u;
+        u.x = pack_bf16(__uint_as_float(a[t * 8 + 0]) * mul, __uint_as_float(a[t * 8 + 1]) * mul);
+        u.y = pack_bf16(__uint_as_float(a[t * 8 + 2]) * mul, __uint_as_float(a[t * 8 + 3]) * mul);
+        u.z = pack_bf16(__uint_as_float(a[t * 8 + 4]) * mul, __uint_as_float(a[t * 8 + 5]) * mul);
+        u.w = pack_bf16(__uint_as_float(a[t * 8 + 6]) * mul, __uint_as_float(a[t * 8 + 7]) * mul);
+        reinterpret_cast<uint4*>(dst + c * 32)[t] = u;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ dK, dV
+template <int HD>
+struct DkvSmem {
+  static constexpr uint32_t TILE = BLK * HD * 2;
+  static constexpr uint32_t K = 0, V = TILE, Q = 2 * TILE, DO = 3 * TILE;
+  static constexpr uint32_t P = 4 * TILE, DS = P + BLK * BLK * 2;
+  static constexpr uint32_t BARS = DS + BLK * BLK * 2;
+  static constexpr uint32_t TOTAL = BARS + 256 + 1024;
+};
+enum DkvBar { KV_FULL = 0, Q_FULL, DO_FULL, Q_EMPTY, DO_EMPTY, SDP_FULL, PDS_READY, PDS_EMPTY, ACC_DONE, NUM_DKV_BARS };
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1)
+attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                 const float* __restrict__ LSE, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
+                 __nv_bfloat16* __restrict__ dV, int S, int Hq, int Hkv, long long lddk, long long lddv,
+                 float scale, float scale_log2, int* status) {
+  using L = DkvSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t bar0 = base + L::BARS;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::BARS + 8 * NUM_DKV_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BARS + 8 * NUM_DKV_BARS + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (S + BLK - 1) / BLK;
+  const int jt = blockIdx.x;  // key tile; early key tiles have the most work and run first
+  const int kv_head = blockIdx.y, batch = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int per_head = n_tiles - jt;
+  const int n_items = G * per_head;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_DKV_BARS; ++i) mbar_init(bar(i), i == PDS_READY ? 128 : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+    tma_prefetch_desc(&tdo);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 256 + HD;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(KV_FULL), 2 * L::TILE);
+      load_tile<HD>(base + L::K, &tk, bar(KV_FULL), kv_head, jt * BLK, batch);
+      load_tile<HD>(base + L::V, &tv, bar(KV_FULL), kv_head, jt * BLK, batch);
+      for (int t = 0; t < n_items; ++t) {
+        const int head = kv_head * G + t / per_head;
+        const int it = jt + t % per_head;
+        if (!mbar_wait(bar(Q_EMPTY), (t & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(Q_FULL), L::TILE);
+        load_tile<HD>(base + L::Q, &tq, bar(Q_FULL), head, it * BLK, batch);
+        if (!mbar_wait(bar(DO_EMPTY), (t & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(DO_FULL), L::TILE);
+        load_tile<HD>(base + L::DO, &tdo, bar(DO_FULL), head, it * BLK, batch);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
+      constexpr uint32_t idesc_g = make_idesc_bf16(BLK, HD, true, true);
+      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
+      for (int t = 0; t < n_items && ok; ++t) {
+        const uint32_t ph = t & 1;
+        if (!mbar_wait(bar(Q_FULL), ph, abort_flag) || !mbar_wait(bar(DO_FULL), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_bf16(t_s, kmajor_desc(base + L::Q, k), kmajor_desc(base + L::K, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_bf16(t_dp, kmajor_desc(base + L::DO, k), kmajor_desc(base + L::V, k), idesc_s, k != 0);
+        umma_commit(bar(SDP_FULL));
+        if (!mbar_wait(bar(PDS_READY), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // dV += P^T dO   (contraction over the 128 query rows)
+#pragma unroll
+        for (int k = 0; k < BLK / 16; ++k)
+          umma_bf16(t_dv, mnmajor_desc(base + L::P, k), mnmajor_desc(base + L::DO, k), idesc_g, (t | k) != 0);
+        umma_commit(bar(DO_EMPTY));
+        // dK += dS^T Q
+#pragma unroll
+        for (int k = 0; k < BLK / 16; ++k)
+          umma_bf16(t_dk, mnmajor_desc(base + L::DS, k), mnmajor_desc(base + L::Q, k), idesc_g, (t | k) != 0);
+        umma_commit(bar(Q_EMPTY));
+        umma_commit(bar(PDS_EMPTY));
+      }
+      if (ok) umma_commit(bar(ACC_DONE));
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    bool ok = true;
+    for (int t = 0; t < n_items; ++t) {
+      const int head = kv_head * G + t / per_head;
+      const int it = jt + t % per_head;
+      const int row = it * BLK + r;
+      const bool row_ok = row < S;
+      const long long stat = (static_cast<long long>(batch) * Hq + head) * S + row;
+      const float lse = row_ok ? LSE[stat] : 0.f;
+      const float dl = row_ok ? delta[stat] : 0.f;
+      if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (t > 0 && !mbar_wait(bar(PDS_EMPTY), (t - 1) & 1, abort_flag)) { ok = false; break; }
+      const bool diag = (it == jt);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+        float p[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool keep = row_ok && (!diag || (c * 32 + i) <= r);
+          p[i] = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
+          ds[i] = p[i] * (__uint_as_float(dv[i]) - dl);
+        }
+        store_row_chunk(smem + L::P, r, c, p);
+        store_row_chunk(smem + L::DS, r, c, ds);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar(PDS_READY));
+    }
+    if (ok && mbar_wait(bar(ACC_DONE), 0, abort_flag)) {
+      tc_fence_after();
+      const int krow = jt * BLK + r;
+      const long long tok = static_cast<long long>(batch) * S + krow;
+      store_acc<HD>(t_dv + lane_addr, dV + tok * lddv + kv_head * HD, 1.f, krow < S);
+      store_acc<HD>(t_dk + lane_addr, dK + tok * lddk + kv_head * HD, scale, krow < S);
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, static_cast<int>(kTimeoutBarrier));
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ dQ
+template <int HD>
+struct DqSmem {
+  static constexpr uint32_t TILE = BLK * HD * 2;
+  static constexpr uint32_t Q = 0, DO = TILE, K = 2 * TILE /*2 stages*/, V = 4 * TILE /*2 stages*/;
+  static constexpr uint32_t DS = 6 * TILE;
+  static constexpr uint32_t BARS = DS + BLK * BLK * 2;
+  static constexpr uint32_t TOTAL = BARS + 256 + 1024;
+};
+enum DqBar { QDO_FULL = 0, DQ_K_FULL0, DQ_K_FULL1, DQ_V_FULL0, DQ_V_FULL1, DQ_KV_EMPTY0, DQ_KV_EMPTY1, DQ_SDP_FULL, DS_READY, DS_EMPTY, DQ_DONE, NUM_DQ_BARS };
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+               const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+               const float* __restrict__ LSE, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
+               int S, int Hq, int Hkv, long long lddq, float scale, float scale_log2, int* status) {
+  using L = DqSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t bar0 = base + L::BARS;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + L::BARS + 8 * NUM_DQ_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::BARS + 8 * NUM_DQ_BARS + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (S + BLK - 1) / BLK;
+  const int qt = n_tiles - 1 - blockIdx.x;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (Hq / Hkv);
+  const int n_kv = qt + 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_DQ_BARS; ++i) mbar_init(bar(i), i == DS_READY ? 128 : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+    tma_prefetch_desc(&tdo);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(QDO_FULL), 2 * L::TILE);
+      load_tile<HD>(base + L::Q, &tq, bar(QDO_FULL), head, qt * BLK, batch);
+      load_tile<HD>(base + L::DO, &tdo, bar(QDO_FULL), head, qt * BLK, batch);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(bar(DQ_KV_EMPTY0 + st), ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(DQ_K_FULL0 + st), L::TILE);
+        load_tile<HD>(base + L::K + st * L::TILE, &tk, bar(DQ_K_FULL0 + st), kv_head, j * BLK, batch);
+        mbar_expect_tx(bar(DQ_V_FULL0 + st), L::TILE);
+        load_tile<HD>(base + L::V + st * L::TILE, &tv, bar(DQ_V_FULL0 + st), kv_head, j * BLK, batch);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
+      constexpr uint32_t idesc_q = make_idesc_bf16(BLK, HD, false, true);
+      bool ok = mbar_wait(bar(QDO_FULL), 0, abort_flag);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(DQ_K_FULL0 + st), ph, abort_flag) || !mbar_wait(bar(DQ_V_FULL0 + st), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk = base + L::K + st * L::TILE, sv = base + L::V + st * L::TILE;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_bf16(t_s, kmajor_desc(base + L::Q, k), kmajor_desc(sk, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_bf16(t_dp, kmajor_desc(base + L::DO, k), kmajor_desc(sv, k), idesc_s, k != 0);
+        umma_commit(bar(DQ_SDP_FULL));
+        if (!mbar_wait(bar(DS_READY), j & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // dQ += dS K_j   (contraction over the 128 key rows)
+#pragma unroll
+        for (int k = 0; k < BLK / 16; ++k)
+          umma_bf16(t_dq, kmajor_desc(base + L::DS, k), mnmajor_desc(sk, k), idesc_q, (j | k) != 0);
+        umma_commit(bar(DQ_KV_EMPTY0 + st));
+        umma_commit(bar(DS_EMPTY));
+      }
+      if (ok) umma_commit(bar(DQ_DONE));
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int row = qt * BLK + r;
+    const bool row_ok = row < S;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const long long stat = (static_cast<long long>(batch) * Hq + head) * S + row;
+    const float lse = row_ok ? LSE[stat] : 0.f;
+    const float dl = row_ok ? delta[stat] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(bar(DQ_SDP_FULL), j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (j > 0 && !mbar_wait(bar(DS_EMPTY), (j - 1) & 1, abort_flag)) { ok = false; break; }
+      const bool diag = (j == qt);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool keep = row_ok && (!diag || (c * 32 + i) <= r);
+          const float p = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
+          ds[i] = p * (__uint_as_float(dv[i]) - dl);
+        }
+        store_row_chunk(smem + L::DS, r, c, ds);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar(DS_READY));
+    }
+    if (ok && mbar_wait(bar(DQ_DONE), 0, abort_flag)) {
+      tc_fence_after();
+      const long long tok = static_cast<long long>(batch) * S + row;
+      store_acc<HD>(t_dq + lane_addr, dQ + tok * lddq + head * HD, scale, row_ok);
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, static_cast<int>(kTimeoutBarrier));
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HD>
+int launch_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+               float* delta, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv, long long ldq,
+               long long ldk, long long ldv, long long lddq, long long lddk, long long lddv, float scale,
+               int* status, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_attn_tensormap(&tq, q, HD, Hq, S, B, ldq)) return -2;
+  if (!make_attn_tensormap(&tk, k, HD, Hkv, S, B, ldk)) return -3;
+  if (!make_attn_tensormap(&tv, v, HD, Hkv, S, B, ldv)) return -4;
+  if (!make_attn_tensormap(&tdo, dout, HD, Hq, S, B, static_cast<long long>(Hq) * HD)) return -5;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         DkvSmem<HD>::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(attn_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<HD>::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaGetLastError();
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const long long warps = static_cast<long long>(B) * S * Hq;
+  attn_delta_kernel<HD><<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq);
+  const int n_tiles = (S + BLK - 1) / BLK;
+  attn_dkdv_kernel<HD><<<dim3(n_tiles, Hkv, B), 192, DkvSmem<HD>::TOTAL, stream>>>(
+      tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), S, Hq, Hkv, lddk,
+      lddv, scale, scale_log2, status);
+  attn_dq_kernel<HD><<<dim3(n_tiles, Hq, B), 192, DqSmem<HD>::TOTAL, stream>>>(
+      tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dq), S, Hq, Hkv, lddq, scale, scale_log2, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace attn
+}  // namespace tft
+
+// Causal attention backward.  dout and o are contiguous [B,S,Hq,hd]; q/k/v as in the forward;
+// dq/dk/dv are written with token strides lddq/lddk/lddv (elements), so they may be views
+// into a fused gradient buffer.  delta is [B,Hq,S] fp32 scratch provided by the caller.
+TFT_API int tft_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                         const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv,
+                         int hd, int ldq, int ldk, int ldv, int lddq, int lddk, int lddv, float scale, int* status,
+                         cudaStream_t stream) {
+  using namespace tft::attn;
+  if (Hq % Hkv || (ldq % 8) || (ldk % 8) || (ldv % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8)) return -1;
+  if (hd == 128)
+    return launch_bwd<128>(dout, q, k, v, o, lse, delta, dq, dk, dv, B, S, Hq, Hkv, ldq, ldk, ldv, lddq, lddk, lddv,
+                           scale, status, stream);
+  if (hd == 64)
+    return launch_bwd<64>(dout, q, k, v, o, lse, delta, dq, dk, dv, B, S, Hq, Hkv, ldq, ldk, ldv, lddq, lddk, lddv,
+                          scale, status, stream);
+  return -1;
+}

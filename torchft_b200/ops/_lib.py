@@ -38,7 +38,7 @@ _PROTOTYPES = {
     "tft_pseudograd": [P, P, L, I, P],
     "tft_nesterov_outer": [P, P, P, L, F, F, I, I, I, P],
     "tft_attn_fwd": [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
-    "tft_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tft_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
 }
 
 
