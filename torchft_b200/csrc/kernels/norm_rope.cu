@@ -167,7 +167,7 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, __nv
 // (the backward pass).  One thread handles 8 consecutive pairs of one (token, head).
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float2* __restrict__ cs,
                             const int* __restrict__ positions, int tokens, int heads, int hd, int row_stride,
-                            float sign) {
+                            float sign, int seq_len) {
   const int half = hd / 2;
   const int vec_per_head = half / 8;
   const long long total = static_cast<long long>(tokens) * heads * vec_per_head;
@@ -176,7 +176,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float2* __restr
   const int v = static_cast<int>(gid % vec_per_head);
   const int head = static_cast<int>((gid / vec_per_head) % heads);
   const int tok = static_cast<int>(gid / (static_cast<long long>(vec_per_head) * heads));
-  const int pos = positions ? positions[tok] : tok;
+  const int pos = positions ? positions[tok] : (seq_len > 0 ? tok % seq_len : tok);
   __nv_bfloat16* base = x + static_cast<size_t>(tok) * row_stride + head * hd + v * 8;
   float a[8], b[8];
   unpack8(*reinterpret_cast<const uint4*>(base), a);
@@ -275,13 +275,13 @@ TFT_API int tft_rope_table(void* cs, int max_pos, int hd, float theta, cudaStrea
 
 // x: [tokens, heads, hd] with token stride row_stride elements; hd % 16 == 0.
 TFT_API int tft_rope(void* x, const void* cs, const int* positions, int tokens, int heads, int hd,
-                     int row_stride, int inverse, cudaStream_t stream) {
+                     int row_stride, int inverse, int seq_len, cudaStream_t stream) {
   if (hd % 16 || row_stride % 8) return static_cast<int>(cudaErrorInvalidValue);
   const long long total = static_cast<long long>(tokens) * heads * (hd / 16);
   const int threads = 256;
   const long long blocks = (total + threads - 1) / threads;
   rope_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
       static_cast<__nv_bfloat16*>(x), static_cast<const float2*>(cs), positions, tokens, heads, hd, row_stride,
-      inverse ? -1.f : 1.f);
+      inverse ? -1.f : 1.f, seq_len);
   return static_cast<int>(cudaGetLastError());
 }

@@ -28,7 +28,7 @@ _PROTOTYPES = {
     "tft_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
     "tft_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
     "tft_rope_table": [P, I, I, F, P],
-    "tft_rope": [P, P, P, I, I, I, I, I, P],
+    "tft_rope": [P, P, P, I, I, I, I, I, I, P],
     "tft_swiglu_fwd": [P, P, L, I, P],
     "tft_swiglu_bwd": [P, P, P, L, I, P],
     "tft_xent": [P, P, P, I, I, I, F, L, P],

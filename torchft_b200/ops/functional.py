@@ -110,19 +110,31 @@ def rmsnorm_bwd(dy, h, w, rstd, dres: Optional[torch.Tensor], dw_out: Optional[t
     return dx, dw
 
 
+def _main_grad_target(weight: torch.Tensor):
+    """``(buffer, accumulate)`` when the parameter carries a preallocated ``main_grad``."""
+    main_grad = getattr(weight, "main_grad", None)
+    if main_grad is None:
+        return None, False
+    acc = bool(getattr(weight, "main_grad_initialized", False))
+    weight.main_grad_initialized = True
+    return main_grad, acc
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps):  # type: ignore[override]
         _check_bf16(x, w)
         y, _, rstd = rmsnorm_fwd(x, w, eps)
         ctx.save_for_backward(x, w, rstd)
+        ctx.weight = w
         return y
 
     @staticmethod
     def backward(ctx, dy):  # type: ignore[override]
         x, w, rstd = ctx.saved_tensors
-        dx, dw = rmsnorm_bwd(dy.contiguous(), x, w, rstd, None)
-        return dx, dw, None
+        dw_out, acc = _main_grad_target(ctx.weight)
+        dx, dw = rmsnorm_bwd(dy.contiguous(), x, w, rstd, None, dw_out, acc)
+        return dx, (None if dw_out is not None else dw), None
 
 
 class _AddRMSNorm(torch.autograd.Function):
@@ -133,14 +145,16 @@ class _AddRMSNorm(torch.autograd.Function):
         _check_bf16(x, res, w)
         y, h, rstd = rmsnorm_fwd(x, w, eps, res)
         ctx.save_for_backward(h, w, rstd)
+        ctx.weight = w
         return y, h
 
     @staticmethod
     def backward(ctx, dy, dh):  # type: ignore[override]
         h, w, rstd = ctx.saved_tensors
         dres = dh.contiguous() if dh is not None else None
-        dx, dw = rmsnorm_bwd(dy.contiguous(), h, w, rstd, dres)
-        return dx, dx, dw, None
+        dw_out, acc = _main_grad_target(ctx.weight)
+        dx, dw = rmsnorm_bwd(dy.contiguous(), h, w, rstd, dres, dw_out, acc)
+        return dx, dx, (None if dw_out is not None else dw), None
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
@@ -163,12 +177,17 @@ def rope_table(max_pos: int, head_dim: int, theta: float, device: torch.device) 
 
 def rope_(x: torch.Tensor, cs: torch.Tensor, heads: int, head_dim: int, inverse: bool = False,
           positions: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rotates ``x[..., heads*head_dim]`` (a view into a wider row is fine) in place."""
+    """Rotates ``x[..., heads*head_dim]`` (a view into a wider row is fine) in place.
+
+    Without ``positions`` (int32, one per token) a 3-D input ``[B, S, ...]`` uses the
+    position inside its sequence and a 2-D input the row index.
+    """
     assert x.dtype == torch.bfloat16 and x.stride(-1) == 1
     tokens = x.numel() // (heads * head_dim)
     row_stride = x.stride(-2) if x.dim() >= 2 else heads * head_dim
+    seq_len = x.shape[-2] if x.dim() >= 3 else 0
     code = _lib.lib().tft_rope(_lib.ptr(x), _lib.ptr(cs), _lib.ptr(positions), tokens, heads, head_dim, row_stride,
-                               1 if inverse else 0, _lib.stream_ptr())
+                               1 if inverse else 0, seq_len, _lib.stream_ptr())
     _lib.check(code, "tft_rope")
     _lib.count_launch()
     return x

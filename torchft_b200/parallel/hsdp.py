@@ -1,0 +1,215 @@
+"""Hybrid-sharded data parallel training engine (HSDP) with per-step fault tolerance.
+
+Layout
+------
+Parameters are grouped into *units* (embedding, one per transformer block, head).  All
+units live in ONE flat bf16 parameter buffer and ONE flat bf16 gradient buffer; module
+parameters are views into the first and carry ``main_grad`` views into the second, so
+weight-gradient GEMMs write their result in place and no flatten / unflatten copy exists.
+
+Inside a replica group of ``S`` GPUs every rank owns the ``1/S`` slice of each unit:
+fp32 AdamW moments exist only for that slice.  A training step is
+
+1. forward / backward on the full (gathered) parameters, which stay resident in HBM,
+2. per unit: reduce-scatter of the gradients over the shard group, then the allreduce of
+   the owned slice over the replica groups (through the ``Manager``: averaged over the
+   participating replicas, errors recorded instead of raised),
+3. ``Manager.should_commit()``; if it passes, fused AdamW on the owned slices and an
+   all-gather of the updated slices.
+
+Steps 2 and 3 use the NVLink peer-memory kernels of ``torchft_b200.parallel.nvlink`` when a
+shard communicator is given; with a single GPU per replica group they reduce to the
+cross-replica allreduce.
+
+The reference composes the same strategy from stock FSDP2 plus its ``ManagedProcessGroup``
+(``torchft/process_group.py:1300-1331``, exercised by ``torchft/fsdp_test.py``); that
+composition is available here too through ``ft_init_device_mesh``.  This engine is the
+B200-first path used by ``bench.py``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from torchft_b200.ops import functional as F
+
+ALIGN = 128  # elements; keeps every unit and every shard 256-byte aligned
+
+
+@dataclass
+class Unit:
+    name: str
+    params: List[nn.Parameter]
+    offset: int  # start inside the flat buffers (elements)
+    numel: int  # padded length (multiple of ALIGN * shard_world)
+
+
+class ShardComm:
+    """Collectives over the GPUs of one replica group (the shard dimension)."""
+
+    rank: int = 0
+    world: int = 1
+
+    def reduce_scatter_(self, full: torch.Tensor, shard_numel: int) -> None:
+        """Sums ``full`` over the group; rank r ends up with the sum in its slice r."""
+
+    def all_gather_(self, full: torch.Tensor, shard_numel: int) -> None:
+        """Every rank's slice r is copied into slice r of every other rank's ``full``."""
+
+
+class HSDPEngine:
+    def __init__(
+        self,
+        model: nn.Module,
+        units: List[Tuple[str, List[nn.Parameter]]],
+        *,
+        manager=None,
+        shard_comm: Optional[ShardComm] = None,
+        lr: float = 3e-4,
+        betas: Tuple[float, float] = (0.9, 0.95),
+        eps: float = 1e-8,
+        weight_decay: float = 0.1,
+        alloc: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None,
+    ) -> None:
+        """
+        Args:
+            units: ``[(name, params)]`` in forward order (``Llama.units()``)
+            manager: ``torchft_b200.Manager`` for the cross-replica dimension (optional)
+            shard_comm: collectives of the shard dimension (``None``: one GPU per group)
+            alloc: allocator for the flat buffers, ``alloc(numel, dtype) -> tensor``; the
+                NVLink backend passes its symmetric-heap allocator so peers can address them
+        """
+        self.model = model
+        self.manager = manager
+        self.comm = shard_comm if shard_comm is not None else ShardComm()
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.opt_step = 0
+        first = units[0][1][0]
+        self.device = first.device
+        S = self.comm.world
+        quantum = ALIGN * S
+
+        self.units: List[Unit] = []
+        cursor = 0
+        for name, params in units:
+            n = sum(-(-p.numel() // 8) * 8 for p in params)
+            n = -(-n // quantum) * quantum
+            self.units.append(Unit(name, list(params), cursor, n))
+            cursor += n
+        self.total = cursor
+
+        if alloc is None:
+            def alloc(numel: int, dtype: torch.dtype) -> torch.Tensor:
+                return torch.zeros(numel, dtype=dtype, device=self.device)
+
+        self.flat_param = alloc(self.total, torch.bfloat16)
+        self.flat_grad = alloc(self.total, torch.bfloat16)
+        # re-point the module parameters into the flat buffers
+        with torch.no_grad():
+            for u in self.units:
+                off = u.offset
+                for p in u.params:
+                    n = p.numel()
+                    view = self.flat_param[off : off + n].view(p.shape)
+                    view.copy_(p.data)
+                    p.data = view
+                    p.main_grad = self.flat_grad[off : off + n].view(p.shape)
+                    p.main_grad_initialized = False
+                    off += -(-n // 8) * 8
+        # optimizer state only for the owned slices, laid out unit after unit
+        self.shard_total = self.total // S
+        self.exp_avg = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
+
+    # ------------------------------------------------------------------ slices
+    def _shard_numel(self, u: Unit) -> int:
+        return u.numel // self.comm.world
+
+    def _own(self, flat: torch.Tensor, u: Unit) -> torch.Tensor:
+        n = self._shard_numel(u)
+        start = u.offset + self.comm.rank * n
+        return flat[start : start + n]
+
+    def _state_slice(self, buf: torch.Tensor, u: Unit) -> torch.Tensor:
+        start = u.offset // self.comm.world
+        return buf[start : start + self._shard_numel(u)]
+
+    # ------------------------------------------------------------------ step pieces
+    def zero_grad(self) -> None:
+        """Gradients are overwritten by the first backward of a step; nothing is cleared."""
+        for u in self.units:
+            for p in u.params:
+                p.main_grad_initialized = False
+                p.grad = None
+
+    def sync_gradients(self) -> None:
+        """Reduce-scatter inside the replica group, then average the owned slices across groups."""
+        futures = []
+        for u in reversed(self.units):  # backward order: the last units finished first
+            full = self.flat_grad[u.offset : u.offset + u.numel]
+            if self.comm.world > 1:
+                self.comm.reduce_scatter_(full, self._shard_numel(u))
+            if self.manager is not None:
+                futures.append(self.manager.allreduce(self._own(self.flat_grad, u)))
+        for f in futures:
+            f.wait()
+
+    def optimizer_step(self, grad_scale: float = 1.0) -> None:
+        """Fused AdamW on the owned slices, then all-gather of the updated parameters."""
+        self.opt_step += 1
+        b1, b2 = self.betas
+        for u in self.units:
+            F.adamw_step_(
+                self._own(self.flat_param, u), self._own(self.flat_grad, u),
+                self._state_slice(self.exp_avg, u), self._state_slice(self.exp_avg_sq, u),
+                lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=self.weight_decay,
+                step=self.opt_step, grad_scale=grad_scale,
+            )
+        self.gather_parameters()
+
+    def gather_parameters(self) -> None:
+        if self.comm.world > 1:
+            for u in self.units:
+                self.comm.all_gather_(self.flat_param[u.offset : u.offset + u.numel], self._shard_numel(u))
+
+    # ------------------------------------------------------------------ whole step
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One fault-tolerant training step; returns the (local) loss tensor."""
+        if self.manager is not None:
+            self.manager.start_quorum()
+        self.zero_grad()
+        loss = self.model(tokens, targets)
+        loss.backward()
+        self.sync_gradients()
+        grad_scale = 1.0 / self.comm.world  # reduce-scatter sums over the shard group
+        if self.manager is None or self.manager.should_commit():
+            self.optimizer_step(grad_scale)
+        return loss.detach()
+
+    # ------------------------------------------------------------------ state for live recovery
+    def state_dict(self) -> Dict[str, object]:
+        """State of THIS rank's slice; rank r of a recovering group pulls it from rank r of a healthy one."""
+        own_params = torch.cat([self._own(self.flat_param, u) for u in self.units]) if self.comm.world > 1 else self.flat_param
+        return {"params": own_params, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq, "opt_step": self.opt_step}
+
+    def load_state_dict(self, sd: Dict[str, object]) -> None:
+        params = sd["params"]
+        assert isinstance(params, torch.Tensor)
+        with torch.no_grad():
+            if self.comm.world > 1:
+                cursor = 0
+                for u in self.units:
+                    n = self._shard_numel(u)
+                    self._own(self.flat_param, u).copy_(params[cursor : cursor + n])
+                    cursor += n
+            else:
+                self.flat_param.copy_(params)
+            self.exp_avg.copy_(sd["exp_avg"])  # type: ignore[arg-type]
+            self.exp_avg_sq.copy_(sd["exp_avg_sq"])  # type: ignore[arg-type]
+        self.opt_step = int(sd["opt_step"])  # type: ignore[arg-type]
+        # every rank of the group loads at the same point of the step, so a collective is safe here
+        self.gather_parameters()
