@@ -1,0 +1,187 @@
+"""NVLink peer-memory collectives and the torchft-nvlink process group on 2+ GPUs.
+
+Every rank is its own process on its own GPU.  The failure test makes a rank stay away
+from a collective (a host-side decision); the survivor's bounded device-side wait runs out
+and is reported as an error status -- no GPU is ever faulted or hung.
+"""
+
+import os
+import sys
+from datetime import timedelta
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _need_gpus(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _spawn(fn, world, *args):
+    from torch.distributed import TCPStore
+
+    store = TCPStore(host_name="127.0.0.1", port=0, is_master=True, wait_for_workers=False)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, store.port, q) + args) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(world):
+        r, ok, payload = q.get(timeout=300)
+        results[r] = (ok, payload)
+    for p in procs:
+        p.join(timeout=60)
+    for r in range(world):
+        ok, payload = results[r]
+        assert ok, f"rank {r} failed: {payload}"
+    return [results[r][1] for r in range(world)]
+
+
+def _entry(fn, rank, world, port, q, *args):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    sys.path.insert(0, ROOT)
+    try:
+        torch.cuda.set_device(rank)
+        out = fn(rank, world, port, *args)
+        q.put((rank, True, out))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, False, f"{e}\n{traceback.format_exc()}"))
+
+
+def _collectives(rank, world, port):
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, SymmetricHeap
+
+    store = PrefixStore("t1", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False))
+    heap = SymmetricHeap.get(256 << 20)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=20))
+    comm.configure(store, rank, world, "epoch-a")
+    out = {}
+    for dtype in (torch.bfloat16, torch.float32):
+        for n in (8, 1000 * 8, (1 << 20) + 8 * 3):
+            t = heap.alloc(n, dtype)
+            g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+            vals = [torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1234 + r)) for r in range(world)]
+            t.copy_(vals[rank].to(dtype))
+            comm.allreduce_(t, 1.0 / world)
+            ref = sum(v.to(dtype).float() for v in vals) / world
+            err = (t.float() - ref).abs().max().item()
+            assert err < (2e-2 if dtype == torch.bfloat16 else 1e-5), (dtype, n, err)
+            # non-contributing rank: zeros instead of its data
+            t.copy_(vals[rank].to(dtype))
+            comm.allreduce_(t, 1.0, contribute=(rank != 0))
+            ref = sum(v.to(dtype).float() for r, v in enumerate(vals) if r != 0)
+            err = (t.float() - ref).abs().max().item()
+            assert err < (4e-2 if dtype == torch.bfloat16 else 1e-5), ("contrib", dtype, n, err)
+    # reduce-scatter + all-gather == allreduce
+    n = world * 4096
+    full = heap.alloc(n, torch.bfloat16)
+    vals = [torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(77 + r)).to(torch.bfloat16) for r in range(world)]
+    full.copy_(vals[rank])
+    comm.reduce_scatter_(full, 1.0)
+    ref = sum(v.float() for v in vals)
+    sl = slice(rank * 4096, (rank + 1) * 4096)
+    assert (full[sl].float() - ref[sl]).abs().max().item() < 4e-2
+    comm.all_gather_(full)
+    assert (full.float() - ref).abs().max().item() < 4e-2
+    b = heap.alloc(1024, torch.float32)
+    b.fill_(float(rank + 1))
+    comm.broadcast_(b, world - 1)
+    assert torch.all(b == float(world)).item()
+    comm.barrier()
+    comm.check()
+    # reconfigure onto a new epoch (same peers) and go again
+    store2 = PrefixStore("t2", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False))
+    comm.configure(store2, (rank + 1) % world, world, "epoch-b")
+    t = heap.alloc(4096, torch.float32)
+    t.fill_(1.0)
+    comm.allreduce_(t, 1.0)
+    assert torch.all(t == float(world)).item()
+    comm.check()
+    return "ok"
+
+
+def test_nvlink_collectives_two_gpus():
+    _need_gpus(2)
+    _spawn(_collectives, 2)
+
+
+def test_nvlink_collectives_four_gpus():
+    _need_gpus(4)
+    _spawn(_collectives, 4)
+
+
+def _process_group(rank, world, port):
+    from torch.distributed import ReduceOp
+
+    from torchft_b200.parallel.nvlink import ProcessGroupNVLink
+
+    pg = ProcessGroupNVLink(timeout=timedelta(seconds=20))
+    pg.configure(f"127.0.0.1:{port}/pg/1", rank, world)
+    assert pg.size() == world and pg.getBackendName() == "torchft-nvlink"
+    t = torch.full((1000,), float(rank + 1), device="cuda")  # not in the heap: staged
+    w = pg.allreduce([t], ReduceOp.SUM)
+    w.get_future().wait()
+    assert torch.all(t == sum(range(1, world + 1))).item()
+    t = torch.full((4099,), float(rank + 1), device="cuda", dtype=torch.bfloat16)
+    w = pg.allreduce_scaled(t, 0.5, contribute=True)
+    w.wait()
+    torch.cuda.synchronize()
+    assert torch.allclose(t.float(), torch.full((4099,), 0.5 * sum(range(1, world + 1)), device="cuda"))
+    outs = [[torch.empty(5, device="cuda") for _ in range(world)]]
+    pg.allgather(outs, [torch.full((5,), float(rank), device="cuda")]).get_future().wait()
+    for r in range(world):
+        assert torch.all(outs[0][r] == float(r)).item()
+    b = torch.full((7,), float(rank), device="cuda")
+    pg.broadcast_one(b, 1).get_future().wait()
+    assert torch.all(b == 1.0).item()
+    return "ok"
+
+
+def test_process_group_nvlink():
+    _need_gpus(2)
+    _spawn(_process_group, 2)
+
+
+def _peer_absent(rank, world, port):
+    """Rank 1 configures but never launches the collective; rank 0's wait must run out cleanly."""
+    import time
+
+    from torch.distributed import ReduceOp, TCPStore
+
+    from torchft_b200.parallel.nvlink import ProcessGroupNVLink
+
+    store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
+    pg = ProcessGroupNVLink(timeout=timedelta(seconds=1))
+    pg.configure(f"127.0.0.1:{port}/absent/1", rank, world)
+    if rank == 0:
+        t = torch.ones(1024, device="cuda")
+        t0 = time.time()
+        fut = pg.allreduce([t], ReduceOp.SUM).get_future()
+        with pytest.raises(TimeoutError, match="device-side wait gave up"):
+            fut.wait()
+        assert time.time() - t0 < 10
+        store.set("rank0_done", b"1")
+        # the context is still healthy: reconfigure alone and keep going
+        pg.configure(f"127.0.0.1:{port}/absent/2", 0, 1)
+        t = torch.ones(8, device="cuda")
+        pg.allreduce_scaled(t, 0.5).get_future().wait()
+        assert torch.all(t == 0.5).item()
+    else:
+        store.get("rank0_done")  # leave only between steps, nothing in flight
+    return "ok"
+
+
+def test_absent_peer_times_out_without_hanging():
+    _need_gpus(2)
+    _spawn(_peer_absent, 2)

@@ -1,0 +1,383 @@
+// Reconfigurable NVLink peer-to-peer collectives.
+//
+// Every rank owns a "symmetric heap": one cudaMalloc'ed region whose CUDA IPC handle is
+// published to the peers, so each rank holds a device pointer to every peer's heap and
+// the same byte offset names the same logical buffer everywhere.  Collectives are single
+// kernels that load from / store to peer heaps directly over NVLink (no NCCL, no copy
+// engine, no multicast objects):
+//
+//   allreduce      two-shot, fused: rank r reduces chunk r from all contributing peers
+//                  (fp32 accumulation), scales it, and stores the result into chunk r of
+//                  EVERY peer in the same pass.  A rank may take part without contributing
+//                  (healing / spare replica): its loads are skipped.
+//   reduce_scatter rank r reduces slice r from all peers into its own buffer.
+//   all_gather     rank r pushes its slice r into every peer's buffer.
+//
+// Synchronisation uses 32-bit flags in a small header of each heap.  A flag value carries
+// the epoch of the current membership (changes on every reconfigure), a sequence number
+// and the sender's contribute bit, so a stale write from an earlier membership can never
+// satisfy a wait.  Every wait is bounded by a wall-clock budget (globaltimer) and also
+// watches a host-mapped abort word; on expiry the kernel records a status and returns.
+#include "common.cuh"
+
+namespace tft {
+namespace p2p {
+
+constexpr int MAX_RANKS = 8;
+constexpr size_t HEADER_BYTES = 4096;  // start pad, end pad, block counter
+// The header holds 16 independent channels of 64 uint32 each, so several communicators
+// (shard group, replica group, ...) can share one heap without touching each other's flags.
+constexpr int CHANNEL_WORDS = 64;
+constexpr int START_PAD = 0;  // uint32 index inside a channel
+constexpr int END_PAD = 16;
+constexpr int DONE_COUNTER = 32;
+
+struct Comm {
+  uint8_t* heap[MAX_RANKS];
+  int rank, world;
+  int pad_base;  // first uint32 of this communicator's channel
+  uint32_t epoch;
+  uint32_t seq;
+  unsigned long long budget_ns;
+  const volatile int* abort_word;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t flag_value(uint32_t epoch, uint32_t seq, uint32_t contrib) {
+  return (epoch << 21) | ((seq & 0xFFFFFu) << 1) | (contrib & 1u);
+}
+
+// Waits until pad[p] (in this rank's own heap) carries (epoch, seq) for every peer.
+// Threads 0..world-1 of the calling block poll; the result is block-uniform.
+// contrib_mask receives one bit per peer.  Returns false on time-out or abort.
+__device__ bool wait_pad(const Comm& c, int pad, uint32_t seq, uint32_t* contrib_mask, int* smem_flag) {
+  if (threadIdx.x == 0) { smem_flag[0] = 1; smem_flag[1] = 0; }
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t* slot = reinterpret_cast<const uint32_t*>(c.heap[c.rank]) + c.pad_base + pad + threadIdx.x;
+    const uint32_t want = flag_value(c.epoch, seq, 0) >> 1;
+    const unsigned long long t0 = now_ns();
+    uint32_t it = 0;
+    while (true) {
+      const uint32_t v = ld_acquire_sys(slot);
+      if ((v >> 1) == want) {
+        if (v & 1u) atomicOr(&smem_flag[1], 1 << threadIdx.x);
+        break;
+      }
+      if ((++it & 63u) == 0) {
+        if (c.abort_word && *c.abort_word) {
+          smem_flag[0] = 0;
+          if (c.status) atomicCAS(c.status, 0, static_cast<int>(kAborted));
+          break;
+        }
+        if (now_ns() - t0 > c.budget_ns) {
+          smem_flag[0] = 0;
+          if (c.status) atomicCAS(c.status, 0, static_cast<int>(kTimeoutPeer));
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (contrib_mask) *contrib_mask = static_cast<uint32_t>(smem_flag[1]);
+  return smem_flag[0] != 0;
+}
+
+// Block 0 announces (epoch, seq, contrib) in the given pad of every peer.
+__device__ __forceinline__ void signal_pad(const Comm& c, int pad, uint32_t seq, uint32_t contrib) {
+  if (threadIdx.x < c.world) {
+    uint32_t* slot = reinterpret_cast<uint32_t*>(c.heap[threadIdx.x]) + c.pad_base + pad + c.rank;
+    st_release_sys(slot, flag_value(c.epoch, seq, contrib));
+  }
+}
+
+// End of a collective: once the last block of this rank is done, tell the peers and wait
+// until every peer said the same (so nobody still touches our heap when the kernel ends).
+__device__ void finish(const Comm& c, int* smem_flag) {
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t* counter = reinterpret_cast<uint32_t*>(c.heap[c.rank]) + c.pad_base + DONE_COUNTER;
+    const uint32_t ticket = atomicAdd(counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (is_last) {
+    signal_pad(c, END_PAD, c.seq, 0);
+    wait_pad(c, END_PAD, c.seq, nullptr, smem_flag);
+  }
+}
+
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static void add(float (&acc)[8], const uint4& v) {
+    acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+    acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+  }
+  __device__ static uint4 pack(const float (&acc)[8], float s) {
+    return make_uint4(__float_as_uint(acc[0] * s), __float_as_uint(acc[1] * s), __float_as_uint(acc[2] * s),
+                      __float_as_uint(acc[3] * s));
+  }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void add(float (&acc)[8], const uint4& v) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+  }
+  __device__ static uint4 pack(const float (&acc)[8], float s) {
+    return make_uint4(pack_bf16(acc[0] * s, acc[1] * s), pack_bf16(acc[2] * s, acc[3] * s),
+                      pack_bf16(acc[4] * s, acc[5] * s), pack_bf16(acc[6] * s, acc[7] * s));
+  }
+};
+
+// In place on heap offset `off`, `nvec` 16-byte vectors.  Rank r owns vectors
+// [r*per, min((r+1)*per, nvec)).
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_kernel(Comm c, size_t off, long long nvec, float scale, int contribute) {
+  __shared__ int flag[2];
+  if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, contribute);
+  uint32_t mask = 0;
+  if (!wait_pad(c, START_PAD, c.seq, &mask, flag)) return;
+  const long long per = (nvec + c.world - 1) / c.world;
+  const long long lo = per * c.rank;
+  const long long hi = lo + per < nvec ? lo + per : nvec;
+  for (long long i = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < hi;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k >= c.world) break;
+      const int p = (c.rank + k) % c.world;  // start with the local copy, then walk the ring
+      if (mask & (1u << p)) Vec<T>::add(acc, ld_peer_v4(c.heap[p] + off + i * 16));
+    }
+    const uint4 out = Vec<T>::pack(acc, scale);
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k >= c.world) break;
+      const int p = (c.rank + k) % c.world;
+      *reinterpret_cast<uint4*>(c.heap[p] + off + i * 16) = out;
+    }
+  }
+  finish(c, flag);
+}
+
+// Slice r = vectors [r*slice_vec, (r+1)*slice_vec) of the buffer at `off`.
+template <typename T>
+__global__ void __launch_bounds__(512)
+reduce_scatter_kernel(Comm c, size_t off, long long slice_vec, float scale) {
+  __shared__ int flag[2];
+  if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, 1);
+  if (!wait_pad(c, START_PAD, c.seq, nullptr, flag)) return;
+  const size_t base = off + static_cast<size_t>(c.rank) * slice_vec * 16;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < slice_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k >= c.world) break;
+      const int p = (c.rank + k) % c.world;
+      Vec<T>::add(acc, ld_peer_v4(c.heap[p] + base + i * 16));
+    }
+    *reinterpret_cast<uint4*>(c.heap[c.rank] + base + i * 16) = Vec<T>::pack(acc, scale);
+  }
+  finish(c, flag);
+}
+
+__global__ void __launch_bounds__(512)
+all_gather_kernel(Comm c, size_t off, long long slice_vec) {
+  __shared__ int flag[2];
+  if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, 1);
+  if (!wait_pad(c, START_PAD, c.seq, nullptr, flag)) return;
+  const size_t base = off + static_cast<size_t>(c.rank) * slice_vec * 16;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < slice_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(c.heap[c.rank] + base + i * 16);
+#pragma unroll
+    for (int k = 1; k < MAX_RANKS; ++k) {
+      if (k >= c.world) break;
+      const int p = (c.rank + k) % c.world;
+      *reinterpret_cast<uint4*>(c.heap[p] + base + i * 16) = v;
+    }
+  }
+  finish(c, flag);
+}
+
+// Root's buffer is copied into every peer (pull by the peers).
+__global__ void __launch_bounds__(512)
+broadcast_kernel(Comm c, size_t off, long long nvec, int root) {
+  __shared__ int flag[2];
+  if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, 1);
+  if (!wait_pad(c, START_PAD, c.seq, nullptr, flag)) return;
+  if (c.rank != root) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      *reinterpret_cast<uint4*>(c.heap[c.rank] + off + i * 16) = ld_peer_v4(c.heap[root] + off + i * 16);
+  }
+  finish(c, flag);
+}
+
+__global__ void barrier_kernel(Comm c) {
+  __shared__ int flag[2];
+  if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, 1);
+  if (!wait_pad(c, START_PAD, c.seq, nullptr, flag)) return;
+  finish(c, flag);
+}
+
+static Comm make_comm(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                      const int* abort_word, int* status) {
+  Comm c;
+  for (int i = 0; i < MAX_RANKS; ++i) c.heap[i] = i < world ? static_cast<uint8_t*>(heaps[i]) : nullptr;
+  c.rank = rank;
+  c.world = world;
+  c.epoch = epoch & 0x7FFu;                                  // bits 0-10: membership epoch
+  c.pad_base = static_cast<int>((epoch >> 16) & 0xFu) * CHANNEL_WORDS;  // bits 16-19: channel
+  c.seq = seq;
+  c.budget_ns = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+  c.abort_word = abort_word;
+  c.status = status;
+  return c;
+}
+
+static int grid_for(long long nvec, int max_blocks) {
+  long long b = (nvec + 511) / 512;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return static_cast<int>(b);
+}
+
+}  // namespace p2p
+}  // namespace tft
+
+using namespace tft::p2p;
+
+TFT_API long long tft_p2p_header_bytes() { return static_cast<long long>(HEADER_BYTES); }
+
+// Allocates a heap (zero-filled) and returns its 64-byte IPC handle.
+TFT_API int tft_p2p_heap_alloc(long long bytes, void** ptr, unsigned char* handle64) {
+  cudaError_t e = cudaMalloc(ptr, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(*ptr, 0, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+TFT_API int tft_p2p_heap_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
+
+TFT_API int tft_p2p_peer_open(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+TFT_API int tft_p2p_peer_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+
+// Pinned host word that kernels poll; the host sets it to 1 to abort waits.
+TFT_API int tft_p2p_abort_word_alloc(int** host_ptr, int** dev_ptr) {
+  cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(host_ptr), sizeof(int), cudaHostAllocMapped);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  **host_ptr = 0;
+  return static_cast<int>(cudaHostGetDevicePointer(reinterpret_cast<void**>(dev_ptr), *host_ptr, 0));
+}
+
+// Clears one channel of the own heap's signalling header (called at reconfigure, before the
+// peers are told about the new membership).
+TFT_API int tft_p2p_reset_channel(void* heap, int channel, cudaStream_t stream) {
+  if (channel < 0 || channel >= 16) return -1;
+  return static_cast<int>(cudaMemsetAsync(static_cast<uint8_t*>(heap) + channel * CHANNEL_WORDS * 4, 0,
+                                          CHANNEL_WORDS * 4, stream));
+}
+
+// dtype: 0 = bf16, 1 = fp32.  Buffer: `bytes` at heap offset `off` (both multiples of 16).
+TFT_API int tft_p2p_allreduce(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                              const int* abort_word, int* status, long long off, long long bytes, int dtype,
+                              float scale, int contribute, int max_blocks, cudaStream_t stream) {
+  if ((off | bytes) & 15) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  const long long nvec = bytes / 16;
+  const int grid = grid_for((nvec + world - 1) / world, max_blocks);
+  if (dtype == 0)
+    allreduce_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(c, static_cast<size_t>(off), nvec, scale, contribute);
+  else
+    allreduce_kernel<float><<<grid, 512, 0, stream>>>(c, static_cast<size_t>(off), nvec, scale, contribute);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The buffer holds `world` slices of slice_bytes each; rank r ends with the scaled sum in slice r.
+TFT_API int tft_p2p_reduce_scatter(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq,
+                                   int timeout_ms, const int* abort_word, int* status, long long off,
+                                   long long slice_bytes, int dtype, float scale, int max_blocks,
+                                   cudaStream_t stream) {
+  if ((off | slice_bytes) & 15) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  const long long nvec = slice_bytes / 16;
+  const int grid = grid_for(nvec, max_blocks);
+  if (dtype == 0)
+    reduce_scatter_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(c, static_cast<size_t>(off), nvec, scale);
+  else
+    reduce_scatter_kernel<float><<<grid, 512, 0, stream>>>(c, static_cast<size_t>(off), nvec, scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+TFT_API int tft_p2p_all_gather(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                               const int* abort_word, int* status, long long off, long long slice_bytes,
+                               int max_blocks, cudaStream_t stream) {
+  if ((off | slice_bytes) & 15) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  const long long nvec = slice_bytes / 16;
+  all_gather_kernel<<<grid_for(nvec, max_blocks), 512, 0, stream>>>(c, static_cast<size_t>(off), nvec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+TFT_API int tft_p2p_broadcast(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                              const int* abort_word, int* status, long long off, long long bytes, int root,
+                              int max_blocks, cudaStream_t stream) {
+  if ((off | bytes) & 15) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  const long long nvec = bytes / 16;
+  broadcast_kernel<<<grid_for(nvec, max_blocks), 512, 0, stream>>>(c, static_cast<size_t>(off), nvec, root);
+  return static_cast<int>(cudaGetLastError());
+}
+
+TFT_API int tft_p2p_barrier(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                            const int* abort_word, int* status, cudaStream_t stream) {
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,482 @@
+"""NVLink peer-memory communication: symmetric heap, communicators, process group.
+
+``SymmetricHeap``       one cudaMalloc'ed region per process, exported with CUDA IPC.  Tensors
+                        carved from it sit at the same offset on every rank, so a kernel
+                        can address any peer's copy.
+``NVLinkCommunicator``  a set of peers that mapped each other's heaps, plus a signalling
+                        channel in the heap header.  ``configure`` re-targets it at a new
+                        membership (handles travel through the quorum's store prefix); its
+                        collectives are single kernels from ``csrc/kernels/p2p_comm.cu``
+                        whose waits are bounded, so a dead peer yields an error status
+                        instead of a hang.
+``ProcessGroupNVLink``  the torchft ``ProcessGroup`` contract on top of it (backend name
+                        ``torchft-nvlink``), with the fused ``allreduce_scaled`` that
+                        ``Manager.allreduce`` uses.
+``NVLinkShardComm``     reduce-scatter / all-gather for the shard dimension of HSDP.
+
+All ranks must live on GPUs of one NVLink/NVSwitch domain (one node).  The reference has
+no counterpart: it delegates to NCCL (``torchft/process_group.py:320-336``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import logging
+import threading
+import time
+import zlib
+from datetime import timedelta
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.distributed import Store
+from torch.distributed.distributed_c10d import ReduceOp, Work
+from torch.futures import Future
+
+from torchft_b200.ops import _lib
+from torchft_b200.process_group import ProcessGroup, _DummyWork, create_store_client
+
+logger = logging.getLogger(__name__)
+
+MAX_RANKS = 8
+_PROTOS_DONE = False
+
+
+def _lib_p2p() -> ctypes.CDLL:
+    global _PROTOS_DONE
+    lib = _lib.lib()
+    if not _PROTOS_DONE:
+        P, I, L, F, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_uint
+        head = [P, I, I, U, U, I, P, P]  # heaps, rank, world, epoch, seq, timeout_ms, abort, status
+        lib.tft_p2p_header_bytes.restype = L
+        lib.tft_p2p_header_bytes.argtypes = []
+        for name, args in {
+            "tft_p2p_heap_alloc": [L, P, P],
+            "tft_p2p_heap_free": [P],
+            "tft_p2p_peer_open": [P, P],
+            "tft_p2p_peer_close": [P],
+            "tft_p2p_abort_word_alloc": [P, P],
+            "tft_p2p_reset_channel": [P, I, P],
+            "tft_p2p_allreduce": head + [L, L, I, F, I, I, P],
+            "tft_p2p_reduce_scatter": head + [L, L, I, F, I, P],
+            "tft_p2p_all_gather": head + [L, L, I, P],
+            "tft_p2p_broadcast": head + [L, L, I, I, P],
+            "tft_p2p_barrier": head + [P],
+        }.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = I
+        _PROTOS_DONE = True
+    return lib
+
+
+class _RawCudaBuffer:
+    """Exposes raw device memory to ``torch.as_tensor`` without copying."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class SymmetricHeap:
+    """Device memory that peers can map.  Bump allocator; nothing is ever freed individually."""
+
+    _instances: Dict[int, "SymmetricHeap"] = {}
+
+    def __init__(self, nbytes: int, device: Optional[torch.device] = None) -> None:
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        lib = _lib_p2p()
+        self.header_bytes = int(lib.tft_p2p_header_bytes())
+        self.nbytes = (int(nbytes) + self.header_bytes + 255) // 256 * 256
+        ptr = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.tft_p2p_heap_alloc(self.nbytes, ctypes.byref(ptr), handle), "tft_p2p_heap_alloc")
+        self.ptr = int(ptr.value)
+        self.handle = bytes(handle)
+        self._bytes = torch.as_tensor(_RawCudaBuffer(self.ptr, self.nbytes), device=self.device)
+        self._cursor = self.header_bytes
+        self._channels = 0
+        self._lock = threading.Lock()
+
+    @classmethod
+    def get(cls, nbytes: int = 1 << 30, device: Optional[torch.device] = None) -> "SymmetricHeap":
+        """Process-wide heap of the current device (created on first use with ``nbytes``)."""
+        idx = torch.cuda.current_device() if device is None else (device.index or 0)
+        heap = cls._instances.get(idx)
+        if heap is None:
+            heap = cls(nbytes, torch.device("cuda", idx))
+            cls._instances[idx] = heap
+        return heap
+
+    def new_channel(self) -> int:
+        with self._lock:
+            ch = self._channels
+            if ch >= 16:
+                raise RuntimeError("all 16 signalling channels of the heap are in use")
+            self._channels += 1
+            return ch
+
+    def free_bytes(self) -> int:
+        return self.nbytes - self._cursor
+
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A zero-initialised 1-D tensor inside the heap (256-byte aligned)."""
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        with self._lock:
+            start = (self._cursor + 255) // 256 * 256
+            if start + nbytes > self.nbytes:
+                raise RuntimeError(
+                    f"symmetric heap exhausted: need {nbytes} bytes, {self.nbytes - start} left of {self.nbytes}"
+                )
+            self._cursor = start + nbytes
+        return self._bytes[start : start + nbytes].view(dtype)
+
+    def offset_of(self, t: torch.Tensor) -> Optional[int]:
+        """Byte offset of ``t`` inside the heap, or None if it lives elsewhere."""
+        p = t.data_ptr()
+        if self.ptr <= p and p + t.numel() * t.element_size() <= self.ptr + self.nbytes:
+            return p - self.ptr
+        return None
+
+
+class _Watcher:
+    """Completes futures once their CUDA event fired, turning a device status into an exception."""
+
+    def __init__(self) -> None:
+        self._cv = threading.Condition()
+        self._items: List[Tuple[torch.cuda.Event, Future, object, torch.Tensor, str]] = []
+        self._thread: Optional[threading.Thread] = None
+
+    def submit(self, event: torch.cuda.Event, fut: Future, result: object, status_host: torch.Tensor, what: str) -> None:
+        with self._cv:
+            if self._thread is None or not self._thread.is_alive():
+                self._thread = threading.Thread(target=self._run, daemon=True, name="tft_nvlink_watcher")
+                self._thread.start()
+            self._items.append((event, fut, result, status_host, what))
+            self._cv.notify()
+
+    def _run(self) -> None:
+        while True:
+            with self._cv:
+                while not self._items:
+                    self._cv.wait()
+                event, fut, result, status_host, what = self._items.pop(0)
+            try:
+                event.synchronize()
+                code = int(status_host.item())
+                if code != 0:
+                    fut.set_exception(TimeoutError(f"{what}: device-side wait gave up (status {code}); a peer is gone or slow"))
+                else:
+                    fut.set_result(result)
+            except Exception as e:  # noqa: BLE001 - forwarded through the future
+                if not fut.done():
+                    fut.set_exception(e)
+
+
+_WATCHER = _Watcher()
+
+
+class _StreamWork(dist._Work):
+    """Work that ran on a side stream: ``wait`` orders the caller's stream after it."""
+
+    def __init__(self, event: torch.cuda.Event, fut: Future) -> None:
+        super().__init__()
+        self._event = event
+        self._fut = fut
+
+    def wait(self, timeout: Optional[timedelta] = None) -> bool:
+        torch.cuda.current_stream().wait_event(self._event)
+        return True
+
+    def get_future(self) -> Future:
+        return self._fut
+
+
+class NVLinkCommunicator:
+    def __init__(self, heap: SymmetricHeap, timeout: timedelta = timedelta(seconds=10), max_blocks: int = 64) -> None:
+        """
+        Args:
+            timeout: budget of every device-side wait (a peer that does not show up within it
+                makes the collective fail with a status instead of hanging)
+            max_blocks: thread blocks per collective kernel (SMs lent to communication)
+        """
+        self.heap = heap
+        self.device = heap.device
+        self.channel = heap.new_channel()
+        self.timeout_ms = max(int(timeout.total_seconds() * 1000), 1)
+        self.max_blocks = max_blocks
+        self.rank = 0
+        self.world = 1
+        self.epoch = 0
+        self.seq = 0
+        self._peers: Dict[bytes, int] = {}  # handle -> mapped pointer (kept open for the process lifetime)
+        self._heaps = (ctypes.c_void_p * MAX_RANKS)()
+        self._heaps[0] = heap.ptr
+        lib = _lib_p2p()
+        host, dev = ctypes.c_void_p(), ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.tft_p2p_abort_word_alloc(ctypes.byref(host), ctypes.byref(dev)), "tft_p2p_abort_word_alloc")
+        self._abort_host = ctypes.cast(host, ctypes.POINTER(ctypes.c_int))
+        self._abort_dev = dev
+        self._status_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.stream = torch.cuda.Stream(device=self.device)
+
+    # ------------------------------------------------------------------ membership
+    def configure(self, store: Store, rank: int, world: int, epoch_key: str) -> None:
+        """Joins the membership identified by ``store`` (a prefix unique to it).
+
+        Exchanges heap handles, maps new peers, clears this communicator's flags and
+        synchronises through the store so nobody signals into a header that is about to
+        be cleared.
+        """
+        if world > MAX_RANKS:
+            raise ValueError(f"at most {MAX_RANKS} ranks per NVLink communicator, got {world}")
+        lib = _lib_p2p()
+        self._abort_host[0] = 0
+        self.rank, self.world = rank, world
+        self.epoch = (zlib.crc32(epoch_key.encode()) & 0x7FF) or 1
+        self.seq = 0
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)  # nothing of the old membership may still run
+            self._status_dev.zero_()
+            _lib.check(lib.tft_p2p_reset_channel(self.heap.ptr, self.channel, _lib.stream_ptr()), "tft_p2p_reset_channel")
+            torch.cuda.synchronize(self.device)
+        if world == 1:
+            self._heaps[0] = self.heap.ptr
+            return
+        store.set(f"handle/{rank}", self.heap.handle)
+        store.set(f"nbytes/{rank}", str(self.heap.nbytes))
+        for r in range(world):
+            if r == rank:
+                self._heaps[r] = self.heap.ptr
+                continue
+            handle = bytes(store.get(f"handle/{r}"))
+            ptr = self._peers.get(handle)
+            if ptr is None:
+                out = ctypes.c_void_p()
+                with torch.cuda.device(self.device):
+                    _lib.check(lib.tft_p2p_peer_open(handle, ctypes.byref(out)), "tft_p2p_peer_open")
+                ptr = int(out.value)
+                self._peers[handle] = ptr
+            self._heaps[r] = ptr
+        # barrier through the store: every header is clean before the first flag is written
+        store.set(f"ready/{rank}", b"1")
+        for r in range(world):
+            store.get(f"ready/{r}")
+
+    def abort(self) -> None:
+        """Makes every wait of kernels in flight give up (host-side kill switch)."""
+        self._abort_host[0] = 1
+
+    # ------------------------------------------------------------------ launch helpers
+    def _head(self):
+        self.seq += 1
+        epoch_word = self.epoch | (self.channel << 16)
+        return (self._heaps, self.rank, self.world, epoch_word, self.seq, self.timeout_ms, self._abort_dev,
+                _lib.ptr(self._status_dev))
+
+    def _offset(self, t: torch.Tensor) -> int:
+        off = self.heap.offset_of(t)
+        if off is None:
+            raise ValueError("tensor does not live in the symmetric heap")
+        assert t.is_contiguous()
+        return off
+
+    def status(self) -> int:
+        """Synchronising read of the device status word (0 = healthy)."""
+        return int(self._status_dev.item())
+
+    def check(self, what: str = "NVLink collective") -> None:
+        code = self.status()
+        if code != 0:
+            raise TimeoutError(f"{what}: device-side wait gave up (status {code}); a peer is gone or slow")
+
+    # ------------------------------------------------------------------ collectives (on the current stream)
+    def allreduce_(self, t: torch.Tensor, scale: float = 1.0, contribute: bool = True) -> None:
+        """In place on a heap tensor: ``t <- scale * sum over contributing ranks``."""
+        if self.world == 1:
+            if not contribute:
+                t.zero_()
+            elif scale != 1.0:
+                t.mul_(scale)
+            return
+        nbytes = t.numel() * t.element_size()
+        assert nbytes % 16 == 0, "buffer length must be a multiple of 16 bytes"
+        dtype = 0 if t.dtype == torch.bfloat16 else 1
+        assert t.dtype in (torch.bfloat16, torch.float32)
+        code = _lib_p2p().tft_p2p_allreduce(*self._head(), self._offset(t), nbytes, dtype, scale, 1 if contribute else 0,
+                                            self.max_blocks, _lib.stream_ptr())
+        _lib.check(code, "tft_p2p_allreduce")
+        _lib.count_launch()
+
+    def reduce_scatter_(self, full: torch.Tensor, scale: float = 1.0) -> None:
+        """``full`` holds ``world`` equal slices; rank r ends with ``scale * sum`` in slice r."""
+        if self.world == 1:
+            if scale != 1.0:
+                full.mul_(scale)
+            return
+        slice_bytes = full.numel() * full.element_size() // self.world
+        assert slice_bytes % 16 == 0
+        dtype = 0 if full.dtype == torch.bfloat16 else 1
+        code = _lib_p2p().tft_p2p_reduce_scatter(*self._head(), self._offset(full), slice_bytes, dtype, scale,
+                                                 self.max_blocks, _lib.stream_ptr())
+        _lib.check(code, "tft_p2p_reduce_scatter")
+        _lib.count_launch()
+
+    def all_gather_(self, full: torch.Tensor) -> None:
+        """Slice r of rank r is pushed into slice r of every peer's ``full``."""
+        if self.world == 1:
+            return
+        slice_bytes = full.numel() * full.element_size() // self.world
+        assert slice_bytes % 16 == 0
+        code = _lib_p2p().tft_p2p_all_gather(*self._head(), self._offset(full), slice_bytes, self.max_blocks, _lib.stream_ptr())
+        _lib.check(code, "tft_p2p_all_gather")
+        _lib.count_launch()
+
+    def broadcast_(self, t: torch.Tensor, root: int) -> None:
+        if self.world == 1:
+            return
+        nbytes = t.numel() * t.element_size()
+        assert nbytes % 16 == 0
+        code = _lib_p2p().tft_p2p_broadcast(*self._head(), self._offset(t), nbytes, root, self.max_blocks, _lib.stream_ptr())
+        _lib.check(code, "tft_p2p_broadcast")
+        _lib.count_launch()
+
+    def barrier(self) -> None:
+        if self.world == 1:
+            return
+        _lib.check(_lib_p2p().tft_p2p_barrier(*self._head(), _lib.stream_ptr()), "tft_p2p_barrier")
+        _lib.count_launch()
+
+
+class ProcessGroupNVLink(ProcessGroup):
+    """Reconfigurable process group over NVLink peer memory (one node, up to 8 GPUs).
+
+    Tensors that live in the symmetric heap are reduced in place; any other CUDA tensor
+    goes through a staging buffer in the heap (two extra local copies).  Collectives run
+    on the communicator's own stream, ordered after the caller's current stream; the
+    returned work's future completes when the kernel finished and fails with
+    ``TimeoutError`` if a device-side wait gave up.
+    """
+
+    def __init__(self, timeout: timedelta = timedelta(seconds=10), heap: Optional[SymmetricHeap] = None,
+                 staging_bytes: int = 256 << 20, max_blocks: int = 64) -> None:
+        super().__init__(0, 1)
+        self._heap = heap if heap is not None else SymmetricHeap.get(max(staging_bytes * 2, 1 << 30))
+        self._comm = NVLinkCommunicator(self._heap, timeout=timeout, max_blocks=max_blocks)
+        self._staging = self._heap.alloc(staging_bytes, torch.uint8)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._configured = False
+
+    @property
+    def communicator(self) -> NVLinkCommunicator:
+        return self._comm
+
+    def configure(self, store_addr: str, rank: int, world_size: int) -> None:
+        store = create_store_client(store_addr)
+        self._comm.configure(store, rank, world_size, epoch_key=store_addr)
+        self._configured = True
+
+    def abort(self) -> None:
+        self._comm.abort()
+
+    def size(self) -> int:
+        return self._comm.world
+
+    def getBackendName(self) -> str:  # noqa: N802
+        return "torchft-nvlink"
+
+    # -- helpers
+    def _launch(self, tensors: List[torch.Tensor], fn, what: str) -> Work:
+        """Runs ``fn(buffer)`` per tensor on the communicator stream (staging when needed)."""
+        if not self._configured:
+            raise RuntimeError("torchft-nvlink process group used before configure()")
+        comm = self._comm
+        current = torch.cuda.current_stream(comm.device)
+        comm.stream.wait_stream(current)
+        with torch.cuda.stream(comm.stream):
+            for t in tensors:
+                assert t.is_cuda and t.is_contiguous(), "NVLink collectives need contiguous CUDA tensors"
+                if comm.world > 1 and self._heap.offset_of(t) is None:
+                    nbytes = t.numel() * t.element_size()
+                    pad = (-nbytes) % 16
+                    if nbytes + pad > self._staging.numel():
+                        raise ValueError(f"tensor of {nbytes} bytes exceeds the staging buffer; allocate it in the heap")
+                    stage = self._staging[: nbytes + pad]
+                    flat = stage[:nbytes].view(t.dtype)
+                    if pad:
+                        stage[nbytes:].zero_()
+                    flat.copy_(t.view(-1))
+                    fn(stage.view(t.dtype))  # the zeroed tail rides along
+                    t.view(-1).copy_(flat)
+                else:
+                    fn(t.view(-1))
+                t.record_stream(comm.stream)
+            self._status_host.copy_(comm._status_dev, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(comm.stream)
+        fut: Future = Future()
+        _WATCHER.submit(event, fut, tensors, self._status_host, what)
+        return _StreamWork(event, fut)
+
+    # -- c10d surface
+    def allreduce(self, tensors: List[torch.Tensor], opts: object) -> Work:
+        op = opts.reduceOp if hasattr(opts, "reduceOp") else opts
+        if op not in (ReduceOp.SUM, ReduceOp.AVG):
+            raise NotImplementedError("torchft-nvlink supports SUM and AVG")
+        scale = 1.0 / self._comm.world if op == ReduceOp.AVG else 1.0
+        return self._launch(tensors, lambda b: self._comm.allreduce_(b, scale), "allreduce")
+
+    def allreduce_scaled(self, tensor: torch.Tensor, scale: float, contribute: bool = True) -> Work:
+        """Sum, scaling and the zero contribution of a non-participating rank in one kernel."""
+        return self._launch([tensor], lambda b: self._comm.allreduce_(b, scale, contribute), "allreduce")
+
+    def broadcast(self, tensor_list: List[torch.Tensor], opts: object) -> Work:
+        root = int(getattr(opts, "rootRank", 0))
+        return self._launch(tensor_list, lambda b: self._comm.broadcast_(b, root), "broadcast")
+
+    def allgather(self, output_tensors: List[List[torch.Tensor]], input_tensor: List[torch.Tensor], opts: object = None) -> Work:
+        comm = self._comm
+        if not self._configured:
+            raise RuntimeError("torchft-nvlink process group used before configure()")
+        current = torch.cuda.current_stream(comm.device)
+        comm.stream.wait_stream(current)
+        with torch.cuda.stream(comm.stream):
+            for outs, inp in zip(output_tensors, input_tensor):
+                nbytes = inp.numel() * inp.element_size()
+                slot = (nbytes + 15) // 16 * 16
+                if slot * comm.world > self._staging.numel():
+                    raise ValueError("allgather exceeds the staging buffer")
+                stage = self._staging[: slot * comm.world]
+                stage[comm.rank * slot : comm.rank * slot + nbytes].view(inp.dtype).copy_(inp.reshape(-1))
+                comm.all_gather_(stage)
+                for r, o in enumerate(outs):
+                    o.view(-1).copy_(stage[r * slot : r * slot + nbytes].view(inp.dtype))
+            self._status_host.copy_(comm._status_dev, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(comm.stream)
+        fut: Future = Future()
+        _WATCHER.submit(event, fut, output_tensors, self._status_host, "allgather")
+        return _StreamWork(event, fut)
+
+
+class NVLinkShardComm:
+    """Shard-dimension collectives of the HSDP engine over a fixed replica-group communicator."""
+
+    def __init__(self, comm: NVLinkCommunicator) -> None:
+        self.comm = comm
+
+    @property
+    def rank(self) -> int:
+        return self.comm.rank
+
+    @property
+    def world(self) -> int:
+        return self.comm.world
+
+    def reduce_scatter_(self, full: torch.Tensor, shard_numel: int) -> None:
+        self.comm.reduce_scatter_(full, 1.0)
+
+    def all_gather_(self, full: torch.Tensor, shard_numel: int) -> None:
+        self.comm.all_gather_(full)
