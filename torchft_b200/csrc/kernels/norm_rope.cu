@@ -5,6 +5,8 @@
 // 16-byte vector accesses, and row statistics stay in registers / shared memory.
 #include "common.cuh"
 
+#include <cstdio>
+
 namespace tft {
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -283,5 +285,94 @@ TFT_API int tft_rope(void* x, const void* cs, const int* positions, int tokens, 
   rope_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
       static_cast<__nv_bfloat16*>(x), static_cast<const float2*>(cs), positions, tokens, heads, hd, row_stride,
       inverse ? -1.f : 1.f, seq_len);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot allocate device memory.
+//
+// tft_rmsnorm_bwd above needs a caller-provided fp32 scratch buffer for the per-block
+// partial sums of the weight gradient.  Some callers have no way to provide one: code that
+// runs inside a region where cudaMalloc is forbidden or would deadlock (for instance a
+// callback of another library's allocator, or a plug-in that is handed raw pointers and a
+// stream and nothing else).  For them the variant below keeps the scratch in a fixed array
+// that is part of this library's device image.  Declared in tft_noalloc.h.
+//
+// Limits and sharing rules:
+//   * dim <= kNoAllocMaxDim (8192); at most kNoAllocParts (148) partial rows are used, so
+//     the array is 148 * 8192 * 4 bytes = 4.6 MiB.  Every GPU on which this library is
+//     loaded holds that much until the process exits.
+//   * All calls on one device share the array and it keeps the last call's contents.  The
+//     backward kernel overwrites every partial row it later reads, so nothing has to be
+//     cleared between calls; but two calls that overlap on the GPU (different streams)
+//     race on it.  Issue them on one stream or order them yourself.
+//   * The first call on each device looks up the array's device address
+//     (cudaGetSymbolAddress).  Make that first call outside of any stream capture.
+//   * No cudaMalloc, cudaFree or allocating library routine is called, ever.
+namespace tft {
+
+constexpr int kNoAllocMaxDim = 8192;
+constexpr int kNoAllocParts = 148;
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocParts * kNoAllocMaxDim];
+
+// Device address of g_noalloc_scratch per device ordinal.  In host code the symbol's name
+// is only a host-side stand-in, so the address is resolved through the runtime, once per
+// device, with that device current.
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+
+static int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace tft
+
+TFT_API int tft_rmsnorm_bwd_noalloc_max_dim() { return tft::kNoAllocMaxDim; }
+
+// Same contract as tft_rmsnorm_bwd minus the scratch argument.  Returns 0 on success,
+// -10 if dim exceeds tft_rmsnorm_bwd_noalloc_max_dim() (a message goes to stderr), another
+// negative / CUDA error code otherwise.
+TFT_API int tft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                    const void* dres, void* dx, void* dw, int rows, int dim, int accumulate,
+                                    cudaStream_t stream) {
+  if (dim > kNoAllocMaxDim) {
+    std::fprintf(stderr,
+                 "tft_rmsnorm_bwd_noalloc: dim %d exceeds the built-in scratch (max %d); use tft_rmsnorm_bwd "
+                 "with a caller-provided buffer\n",
+                 dim, kNoAllocMaxDim);
+    return -10;
+  }
+  int threads = 0;
+  const int vpt = norm_config(dim, &threads);
+  if (!vpt || rows <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  const int parts = rows < kNoAllocParts ? rows : kNoAllocParts;
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+  switch (vpt) {
+    case 1: rmsnorm_bwd_kernel<1><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
+    case 2: rmsnorm_bwd_kernel<2><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
+    case 3: rmsnorm_bwd_kernel<3><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
+    default: rmsnorm_bwd_kernel<4><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
+  }
+  rmsnorm_dw_reduce_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(scratch, static_cast<__nv_bfloat16*>(dw), parts,
+                                                                  dim, accumulate);
   return static_cast<int>(cudaGetLastError());
 }
