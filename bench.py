@@ -129,6 +129,7 @@ def run_ours(args: argparse.Namespace) -> None:
     from torchft_b200.ops import _lib
     from torchft_b200.parallel.hsdp import HSDPEngine
     from torchft_b200.parallel.nvlink import NVLinkCommunicator, NVLinkShardComm, ProcessGroupNVLink, SymmetricHeap
+    from torchft_b200.parallel.nvlink_heal import NVLinkCheckpointTransport
     from torch.distributed import PrefixStore, TCPStore
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -173,7 +174,9 @@ def run_ours(args: argparse.Namespace) -> None:
 
     # ---- memory: flat parameters and gradients live in the NVLink-visible heap
     n_params = cfg.num_params()
-    heap_bytes = 2 * 2 * (n_params + 64 * 1024 * (cfg.n_layers + 2)) + (1 << 30)
+    padded = n_params + 64 * 1024 * (cfg.n_layers + 2)
+    # bf16 parameters + bf16 gradients (full) and the fp32 AdamW moments of the owned slices
+    heap_bytes = 2 * 2 * padded + 2 * 4 * (padded // shard_world + 1024) + (1 << 30)
     heap = SymmetricHeap.get(heap_bytes, device)
     shard = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
     client_store = TCPStore("127.0.0.1", store_port, is_master=False, wait_for_workers=False)
@@ -198,6 +201,8 @@ def run_ours(args: argparse.Namespace) -> None:
         lighthouse_addr=lighthouse_addr,
         replica_id=f"bench_{group}_",
         hostname="127.0.0.1",
+        # step-0 weight sync and any later recovery move GPU to GPU over NVLink
+        checkpoint_transport=NVLinkCheckpointTransport(heap, timeout=timedelta(seconds=120)),
     )
     engine = HSDPEngine(
         model, model.units(), manager=manager, shard_comm=NVLinkShardComm(shard),

@@ -381,3 +381,29 @@ TFT_API int tft_p2p_barrier(void* const* heaps, int rank, int world, unsigned ep
   barrier_kernel<<<1, 32, 0, stream>>>(c);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------
+// Live-recovery copy: a recovering rank pulls state straight out of a healthy peer's heap.
+// No flags are involved (the control plane holds the source's checkpoint gate open while
+// the copy runs), so the kernel contains no wait at all.
+namespace tft {
+namespace p2p {
+
+__global__ void __launch_bounds__(512) pull_copy_kernel(uint8_t* __restrict__ dst, const uint8_t* src, long long nvec) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    *reinterpret_cast<uint4*>(dst + i * 16) = ld_peer_v4(src + i * 16);
+}
+
+}  // namespace p2p
+}  // namespace tft
+
+// dst: local device memory, src: peer-mapped device memory; both 16-byte aligned, bytes % 16 == 0.
+TFT_API int tft_p2p_pull(void* dst, const void* src, long long bytes, int max_blocks, cudaStream_t stream) {
+  if ((bytes & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return -1;
+  if (bytes == 0) return 0;
+  const long long nvec = bytes / 16;
+  tft::p2p::pull_copy_kernel<<<grid_for(nvec, max_blocks), 512, 0, stream>>>(
+      static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nvec);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -172,6 +172,11 @@ class Manager:
         self._replica_rank: int = 0
         self._replica_world_size: int = 0
 
+        # Transports that can receive in place (NVLink) ask the manager for the live state.
+        bind = getattr(self._checkpoint_transport, "bind_manager", None)
+        if callable(bind):
+            bind(self)
+
     # ------------------------------------------------------------------ state dict plumbing
     def set_state_dict_fns(self, load_state_dict: Callable[[T], None], state_dict: Callable[[], T]) -> None:
         self._load_state_dict = load_state_dict

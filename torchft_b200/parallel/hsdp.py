@@ -122,8 +122,8 @@ class HSDPEngine:
                     off += -(-n // 8) * 8
         # optimizer state only for the owned slices, laid out unit after unit
         self.shard_total = self.total // S
-        self.exp_avg = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
-        self.exp_avg_sq = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
+        self.exp_avg = alloc(self.shard_total, torch.float32)
+        self.exp_avg_sq = alloc(self.shard_total, torch.float32)
 
     # ------------------------------------------------------------------ slices
     def _shard_numel(self, u: Unit) -> int:
@@ -193,23 +193,24 @@ class HSDPEngine:
     # ------------------------------------------------------------------ state for live recovery
     def state_dict(self) -> Dict[str, object]:
         """State of THIS rank's slice; rank r of a recovering group pulls it from rank r of a healthy one."""
-        own_params = torch.cat([self._own(self.flat_param, u) for u in self.units]) if self.comm.world > 1 else self.flat_param
+        # views, not copies: an NVLink transport moves them peer to peer without staging
+        own_params = [self._own(self.flat_param, u) for u in self.units]
         return {"params": own_params, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq, "opt_step": self.opt_step}
 
     def load_state_dict(self, sd: Dict[str, object]) -> None:
         params = sd["params"]
-        assert isinstance(params, torch.Tensor)
+        assert isinstance(params, (list, tuple)) and len(params) == len(self.units)
+
+        def put(dst: torch.Tensor, src: torch.Tensor) -> None:
+            # an in-place transport hands back our own tensors: nothing to copy then
+            if src.data_ptr() != dst.data_ptr():
+                dst.copy_(src.to(dst.device, non_blocking=True))
+
         with torch.no_grad():
-            if self.comm.world > 1:
-                cursor = 0
-                for u in self.units:
-                    n = self._shard_numel(u)
-                    self._own(self.flat_param, u).copy_(params[cursor : cursor + n])
-                    cursor += n
-            else:
-                self.flat_param.copy_(params)
-            self.exp_avg.copy_(sd["exp_avg"])  # type: ignore[arg-type]
-            self.exp_avg_sq.copy_(sd["exp_avg_sq"])  # type: ignore[arg-type]
+            for u, src in zip(self.units, params):
+                put(self._own(self.flat_param, u), src)
+            put(self.exp_avg, sd["exp_avg"])  # type: ignore[arg-type]
+            put(self.exp_avg_sq, sd["exp_avg_sq"])  # type: ignore[arg-type]
         self.opt_step = int(sd["opt_step"])  # type: ignore[arg-type]
         # every rank of the group loads at the same point of the step, so a collective is safe here
         self.gather_parameters()
