@@ -185,3 +185,115 @@ def _peer_absent(rank, world, port):
 def test_absent_peer_times_out_without_hanging():
     _need_gpus(2)
     _spawn(_peer_absent, 2)
+
+
+def _hsdp_shards(rank, world, port):
+    """One replica group sharded over `world` GPUs must match one GPU fed the concatenated batch."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.models.llama import Llama, LlamaConfig
+    from torchft_b200.parallel.hsdp import HSDPEngine
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, NVLinkShardComm, SymmetricHeap
+
+    cfg = LlamaConfig.tiny()
+    heap = SymmetricHeap.get(512 << 20)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=30))
+    comm.configure(PrefixStore("hsdp", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)), rank, world, "hsdp")
+
+    gen = torch.Generator().manual_seed(5)
+    tokens = torch.randint(cfg.vocab_size, (world, 256), generator=gen).cuda()
+    targets = torch.randint(cfg.vocab_size, (world, 256), generator=gen).cuda()
+
+    ref_model = Llama(cfg, device="cuda")
+    ref_model.init_weights(seed=3)
+    ref = HSDPEngine(ref_model, ref_model.units(), lr=1e-3)
+    model = Llama(cfg, device="cuda")
+    model.init_weights(seed=3)
+    engine = HSDPEngine(model, model.units(), shard_comm=NVLinkShardComm(comm), lr=1e-3, alloc=heap.alloc)
+    assert engine.exp_avg.numel() * world == engine.total
+    for _ in range(3):
+        ref.train_step(tokens, targets)
+        engine.train_step(tokens[rank : rank + 1], targets[rank : rank + 1])
+    torch.cuda.synchronize()
+    comm.check()
+    a, b = engine.flat_param.float(), ref.flat_param.float()
+    err = (a - b).abs().max().item()
+    assert err < 2e-2, f"sharded and single-GPU parameters differ by {err}"
+    return "ok"
+
+
+def test_hsdp_engine_sharded_matches_single_gpu():
+    _need_gpus(2)
+    _spawn(_hsdp_shards, 2)
+
+
+def _replicas_with_manager(rank, world, port):
+    """Two replica groups of one GPU: lighthouse quorum, step-0 heal over NVLink, fused allreduce."""
+    from torch.distributed import TCPStore
+
+    from torchft_b200 import _control
+    from torchft_b200.manager import Manager
+    from torchft_b200.models.llama import Llama, LlamaConfig
+    from torchft_b200.parallel.hsdp import HSDPEngine
+    from torchft_b200.parallel.nvlink import ProcessGroupNVLink, SymmetricHeap
+    from torchft_b200.parallel.nvlink_heal import NVLinkCheckpointTransport
+
+    _control.set_log_enabled(False)
+    store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
+    lighthouse = None
+    if rank == 0:
+        lighthouse = _control.Lighthouse(bind="[::]:0", min_replicas=world, join_timeout_ms=20000, quorum_tick_ms=10)
+        store.set("lighthouse", lighthouse.address())
+    lighthouse_addr = store.get("lighthouse").decode()
+    group_store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+
+    cfg = LlamaConfig.tiny()
+    heap = SymmetricHeap.get(512 << 20)
+    model = Llama(cfg, device="cuda")
+    model.init_weights(seed=100 + rank)  # replicas start DIFFERENT: the step-0 heal must fix that
+    box = {}
+    transport = NVLinkCheckpointTransport(heap, timeout=timedelta(seconds=30))
+    manager = Manager(
+        pg=ProcessGroupNVLink(timeout=timedelta(seconds=30), heap=heap, staging_bytes=16 << 20),
+        load_state_dict=lambda sd: box["e"].load_state_dict(sd),
+        state_dict=lambda: box["e"].state_dict(),
+        min_replica_size=world,
+        timeout=timedelta(seconds=30),
+        quorum_timeout=timedelta(seconds=30),
+        rank=0,
+        world_size=1,
+        store_addr="127.0.0.1",
+        store_port=group_store.port,
+        lighthouse_addr=lighthouse_addr,
+        replica_id=f"replica_{rank}_",
+        hostname="127.0.0.1",
+        checkpoint_transport=transport,
+    )
+    engine = HSDPEngine(model, model.units(), manager=manager, lr=1e-3, alloc=heap.alloc)
+    box["e"] = engine
+    gen = torch.Generator().manual_seed(50 + rank)
+    tokens = torch.randint(cfg.vocab_size, (1, 256), generator=gen).cuda()
+    targets = torch.randint(cfg.vocab_size, (1, 256), generator=gen).cuda()
+    for _ in range(4):
+        engine.train_step(tokens, targets)
+    torch.cuda.synchronize()
+    assert manager.current_step() == 4, manager.current_step()
+    digest = engine.flat_param.float().double().sum().item()
+    store.set(f"digest/{rank}", str(digest))
+    digests = [float(store.get(f"digest/{r}").decode()) for r in range(world)]
+    pulled = transport.bytes_pulled
+    store.set(f"done/{rank}", b"1")
+    for r in range(world):
+        store.get(f"done/{r}")
+    manager.shutdown(wait=False)
+    if lighthouse is not None:
+        lighthouse.shutdown()
+    assert all(abs(d - digests[0]) <= 1e-6 * max(1.0, abs(digests[0])) for d in digests), digests
+    return pulled
+
+
+def test_two_replicas_quorum_heal_and_allreduce_on_gpus():
+    _need_gpus(2)
+    pulled = _spawn(_replicas_with_manager, 2)
+    # exactly one of the two replicas healed from the other at step 0, GPU to GPU
+    assert sorted(p > 0 for p in pulled) == [False, True]

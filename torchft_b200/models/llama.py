@@ -149,6 +149,10 @@ class Llama(nn.Module):
         self.norm = nn.Parameter(torch.ones(cfg.dim, **kw))
         self.output = nn.Parameter(torch.empty(cfg.vocab_size, cfg.dim, **kw))
         self._cs: Optional[torch.Tensor] = None
+        # Called during backward with a unit name ("layer7", "head") as soon as all weight
+        # gradients of that unit are final; an engine uses it to start communicating them
+        # while the rest of the backward pass still runs.
+        self.unit_grad_ready = None
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0) -> None:
@@ -179,8 +183,15 @@ class Llama(nn.Module):
         cs = self.rope_cache(tokens.device)
         x = F.embedding(tokens, self.tok_embeddings)
         residual = None
-        for layer in self.layers:
+        hook = self.unit_grad_ready if torch.is_grad_enabled() else None
+        for i, layer in enumerate(self.layers):
+            if hook is not None and x.requires_grad:
+                # the gradient w.r.t. a block's input is the last thing its backward produces,
+                # so when it arrives every weight gradient of that block is complete
+                x.register_hook(lambda g, name=f"layer{i}": hook(name))
             x, residual = layer(x, residual, cs)
+        if hook is not None and x.requires_grad:
+            x.register_hook(lambda g: hook("head"))
         xn, _ = F.add_rmsnorm(x, residual, self.norm, self.cfg.norm_eps)
         logits = F.linear(xn, self.output)
         if targets is None:

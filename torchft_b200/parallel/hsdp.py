@@ -124,6 +124,13 @@ class HSDPEngine:
         self.shard_total = self.total // S
         self.exp_avg = alloc(self.shard_total, torch.float32)
         self.exp_avg_sq = alloc(self.shard_total, torch.float32)
+        # communication of finished units overlaps the rest of the backward pass on this stream
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        self._by_name = {u.name: u for u in self.units}
+        self._synced: set = set()
+        self._futures: list = []
+        if hasattr(model, "unit_grad_ready"):
+            model.unit_grad_ready = self._unit_grad_ready
 
     # ------------------------------------------------------------------ slices
     def _shard_numel(self, u: Unit) -> int:
@@ -145,18 +152,43 @@ class HSDPEngine:
             for p in u.params:
                 p.main_grad_initialized = False
                 p.grad = None
+        self._synced = set()
+        self._futures = []
 
-    def sync_gradients(self) -> None:
-        """Reduce-scatter inside the replica group, then average the owned slices across groups."""
-        futures = []
-        for u in reversed(self.units):  # backward order: the last units finished first
+    def _sync_unit(self, u: Unit) -> None:
+        """Queues the communication of one unit's gradients on the communication stream."""
+        if u.name in self._synced:
+            return
+        self._synced.add(u.name)
+        if self.comm.world == 1 and self.manager is None:
+            return
+        current = torch.cuda.current_stream(self.device)
+        self.comm_stream.wait_stream(current)
+        with torch.cuda.stream(self.comm_stream):
             full = self.flat_grad[u.offset : u.offset + u.numel]
             if self.comm.world > 1:
                 self.comm.reduce_scatter_(full, self._shard_numel(u))
             if self.manager is not None:
-                futures.append(self.manager.allreduce(self._own(self.flat_grad, u)))
-        for f in futures:
+                self._futures.append(self.manager.allreduce(self._own(self.flat_grad, u)))
+
+    def _unit_grad_ready(self, name: str) -> None:
+        """Backward-time callback of the model: the named unit's gradients are final."""
+        u = self._by_name.get(name)
+        if u is not None:
+            self._sync_unit(u)
+
+    def sync_gradients(self) -> None:
+        """Reduce-scatter inside the replica group, then average the owned slices across groups.
+
+        Units whose gradients were announced during backward are already in flight; the rest
+        (at least the embedding, whose gradient is complete only when backward returns) go now.
+        """
+        for u in reversed(self.units):  # backward order: the last units finished first
+            self._sync_unit(u)
+        for f in self._futures:
             f.wait()
+        self._futures = []
+        torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
 
     def optimizer_step(self, grad_scale: float = 1.0) -> None:
         """Fused AdamW on the owned slices, then all-gather of the updated parameters."""

@@ -77,6 +77,7 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
         self._step = -1
         self._state_dict: Optional[Dict[str, Any]] = None
         self._leases: Dict[str, threading.Event] = {}
+        self._ready_event: Optional[torch.cuda.Event] = None
         self._leases_lock = threading.Lock()
         self._targets_fn: Optional[Callable[[], Dict[str, Any]]] = None
         self._peers: Dict[bytes, int] = {}
@@ -122,8 +123,11 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
                             "heap_bytes": transport._heap.nbytes,
                             "state": _describe(transport._state_dict, transport._heap),
                         }
-                        # everything the copy will read must be complete on the device
-                        torch.cuda.synchronize(transport._heap.device)
+                        # Everything the copy will read was queued before the gate opened; wait for
+                        # exactly that work.  (A full device synchronisation could wait on a
+                        # collective that itself waits for the receiver: a cycle.)
+                        if transport._ready_event is not None:
+                            transport._ready_event.synchronize()
                         self._reply(200, pickle.dumps(manifest))
                         # hold the gate until the receiver reports that its copy finished
                         if not done.wait(transport._timeout.total_seconds()):
@@ -177,6 +181,9 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
 
     def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: Dict[str, Any], timeout: timedelta) -> None:
         self._state_dict = state_dict
+        with torch.cuda.device(self._heap.device):
+            self._ready_event = torch.cuda.Event()
+            self._ready_event.record(torch.cuda.current_stream())
         self.allow_checkpoint(step)
 
     def _peer_ptr(self, handle: bytes) -> int:
