@@ -1,0 +1,68 @@
+"""The example trainer and the lighthouse CLI, end to end on CPU (three real processes)."""
+
+import os
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_train_ddp_example_two_replica_groups():
+    lh_port = _free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", TORCHFT_B200_LOG="")
+    lighthouse = subprocess.Popen(
+        [sys.executable, "-m", "torchft_b200.lighthouse", "--min_replicas", "2", "--bind", f"[::]:{lh_port}",
+         "--join_timeout_ms", "20000"],
+        env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL,
+    )
+    workers = []
+    try:
+        for _ in range(100):
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{lh_port}/status", timeout=1).read()
+                break
+            except Exception:
+                time.sleep(0.1)
+        for g in range(2):
+            wenv = dict(env, REPLICA_GROUP_ID=str(g), NUM_REPLICA_GROUPS="2", TOTAL_STEPS="5", RANK="0", WORLD_SIZE="1",
+                        MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
+                        TORCHFT_LIGHTHOUSE=f"http://127.0.0.1:{lh_port}")
+            # each replica group has its own store; here the worker hosts it itself
+            code = (
+                "import os, torch.distributed as dist\n"
+                "store = dist.TCPStore('127.0.0.1', int(os.environ['MASTER_PORT']), is_master=True, wait_for_workers=False)\n"
+                "import runpy; runpy.run_path(os.path.join(%r, 'train_ddp.py'), run_name='__main__')\n" % ROOT
+            )
+            workers.append(subprocess.Popen([sys.executable, "-c", code], env=wenv, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+        for w in workers:
+            out, _ = w.communicate(timeout=240)
+            assert w.returncode == 0, out.decode()[-3000:]
+        status = urllib.request.urlopen(f"http://127.0.0.1:{lh_port}/status", timeout=5).read().decode()
+        assert "train_ddp_0" in status and "train_ddp_1" in status
+    finally:
+        for w in workers:
+            if w.poll() is None:
+                w.kill()
+        lighthouse.kill()
+        lighthouse.wait()
+
+
+def test_standalone_lighthouse_binary_usage():
+    from torchft_b200.utils import build
+
+    exe = build.lighthouse_bin_path()
+    if not exe.exists():
+        build.build_control()
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=30)
+    assert res.returncode == 2 and "min_replicas is required" in res.stderr

@@ -106,7 +106,11 @@ py::dict quorum_to_dict(const wire::Quorum& q) {
 
 }  // namespace
 
-PYBIND11_MODULE(_control, m) {
+#ifndef TFT_MODULE_NAME
+#define TFT_MODULE_NAME _control
+#endif
+// TFT_MODULE_NAME lets the same bindings be built under another module name.
+PYBIND11_MODULE(TFT_MODULE_NAME, m) {
   m.doc() = "C++ control plane: lighthouse, manager server and clients";
 
   py::class_<QuorumResult>(m, "QuorumResult")

@@ -89,7 +89,7 @@ struct DkvSmem {
 enum DkvBar { KV_FULL = 0, Q_FULL, DO_FULL, Q_EMPTY, DO_EMPTY, SDP_FULL, PDS_READY, PDS_EMPTY, ACC_DONE, NUM_DKV_BARS };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                  const float* __restrict__ LSE, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
@@ -107,14 +107,16 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (S + BLK - 1) / BLK;
-  const int jt = blockIdx.x;  // key tile; early key tiles have the most work and run first
-  const int kv_head = blockIdx.y, batch = blockIdx.z;
+  // Blocks are numbered heaviest first over ALL heads (longest-processing-time order), so the
+  // hardware scheduler hands late SMs the short tiles instead of a long straggler.
+  const int jt = blockIdx.x / Hkv;  // key tile; early key tiles have the most work
+  const int kv_head = blockIdx.x % Hkv, batch = blockIdx.y;
   const int G = Hq / Hkv;
   const int per_head = n_tiles - jt;
   const int n_items = G * per_head;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_DKV_BARS; ++i) mbar_init(bar(i), i == PDS_READY ? 128 : 1);
+    for (int i = 0; i < NUM_DKV_BARS; ++i) mbar_init(bar(i), i == PDS_READY ? 256 : 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq);
@@ -182,6 +184,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;  // two threads per row: columns [0,64) and [64,128)
     const int r = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     bool ok = true;
@@ -198,7 +201,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (t > 0 && !mbar_wait(bar(PDS_EMPTY), (t - 1) & 1, abort_flag)) { ok = false; break; }
       const bool diag = (it == jt);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
         tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
@@ -221,8 +224,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       tc_fence_after();
       const int krow = jt * BLK + r;
       const long long tok = static_cast<long long>(batch) * S + krow;
-      store_acc<HD>(t_dv + lane_addr, dV + tok * lddv + kv_head * HD, 1.f, krow < S);
-      store_acc<HD>(t_dk + lane_addr, dK + tok * lddk + kv_head * HD, scale, krow < S);
+      store_acc<HD / 2>(t_dv + lane_addr + half * (HD / 2), dV + tok * lddv + kv_head * HD + half * (HD / 2), 1.f, krow < S);
+      store_acc<HD / 2>(t_dk + lane_addr + half * (HD / 2), dK + tok * lddk + kv_head * HD + half * (HD / 2), scale, krow < S);
     }
     tc_fence_before();
   }
@@ -252,7 +255,7 @@ struct DqSmem {
 enum DqBar { QDO_FULL = 0, DQ_K_FULL0, DQ_K_FULL1, DQ_V_FULL0, DQ_V_FULL1, DQ_KV_EMPTY0, DQ_KV_EMPTY1, DQ_SDP_FULL, DS_READY, DS_EMPTY, DQ_DONE, NUM_DQ_BARS };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                const float* __restrict__ LSE, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
@@ -269,13 +272,13 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (S + BLK - 1) / BLK;
-  const int qt = n_tiles - 1 - blockIdx.x;
-  const int head = blockIdx.y, batch = blockIdx.z;
+  const int qt = n_tiles - 1 - blockIdx.x / Hq;  // heaviest first over all heads
+  const int head = blockIdx.x % Hq, batch = blockIdx.y;
   const int kv_head = head / (Hq / Hkv);
   const int n_kv = qt + 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_DQ_BARS; ++i) mbar_init(bar(i), i == DS_READY ? 128 : 1);
+    for (int i = 0; i < NUM_DQ_BARS; ++i) mbar_init(bar(i), i == DS_READY ? 256 : 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq);
@@ -338,6 +341,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;  // two threads per row: columns [0,64) and [64,128)
     const int r = q * 32 + lane;
     const int row = qt * BLK + r;
     const bool row_ok = row < S;
@@ -352,7 +356,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
       if (j > 0 && !mbar_wait(bar(DS_EMPTY), (j - 1) & 1, abort_flag)) { ok = false; break; }
       const bool diag = (j == qt);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
         tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
@@ -373,7 +377,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
     if (ok && mbar_wait(bar(DQ_DONE), 0, abort_flag)) {
       tc_fence_after();
       const long long tok = static_cast<long long>(batch) * S + row;
-      store_acc<HD>(t_dq + lane_addr, dQ + tok * lddq + head * HD, scale, row_ok);
+      store_acc<HD / 2>(t_dq + lane_addr + half * (HD / 2), dQ + tok * lddq + head * HD + half * (HD / 2), scale, row_ok);
     }
     tc_fence_before();
   }
@@ -416,10 +420,10 @@ int launch_bwd(const void* dout, const void* q, const void* k, const void* v, co
   attn_delta_kernel<HD><<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq);
   const int n_tiles = (S + BLK - 1) / BLK;
-  attn_dkdv_kernel<HD><<<dim3(n_tiles, Hkv, B), 192, DkvSmem<HD>::TOTAL, stream>>>(
+  attn_dkdv_kernel<HD><<<dim3(n_tiles * Hkv, B, 1), 320, DkvSmem<HD>::TOTAL, stream>>>(
       tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), S, Hq, Hkv, lddk,
       lddv, scale, scale_log2, status);
-  attn_dq_kernel<HD><<<dim3(n_tiles, Hq, B), 192, DqSmem<HD>::TOTAL, stream>>>(
+  attn_dq_kernel<HD><<<dim3(n_tiles * Hq, B, 1), 320, DqSmem<HD>::TOTAL, stream>>>(
       tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dq), S, Hq, Hkv, lddq, scale, scale_log2, status);
   return static_cast<int>(cudaGetLastError());
 }

@@ -47,8 +47,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qtiles = (S + BLK - 1) / BLK;
-  const int qt = n_qtiles - 1 - blockIdx.x;  // heavy (late) tiles are scheduled first
-  const int head = blockIdx.y, batch = blockIdx.z;
+  const int qt = n_qtiles - 1 - blockIdx.x / Hq;  // heaviest tiles first, over all heads
+  const int head = blockIdx.x % Hq, batch = blockIdx.y;
   const int kv_head = head / (Hq / Hkv);
   const int n_kv = qt + 1;
 
@@ -247,7 +247,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
     configured = true;
   }
   cudaGetLastError();
-  dim3 grid((S + BLK - 1) / BLK, Hq, B);
+  dim3 grid(((S + BLK - 1) / BLK) * Hq, B, 1);
   kfn<<<grid, 192, FwdSmem<HD>::TOTAL, stream>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(o), lse, S, Hq, Hkv, ldo,
                                                  scale * 1.4426950408889634f, status);
   return static_cast<int>(cudaGetLastError());
