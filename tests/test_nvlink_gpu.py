@@ -216,6 +216,8 @@ def _hsdp_shards(rank, world, port):
         engine.train_step(tokens[rank : rank + 1], targets[rank : rank + 1])
     torch.cuda.synchronize()
     comm.check()
+    engine.gather_parameters()  # slices updated by the last step are exchanged at the start of the next one
+    torch.cuda.synchronize()
     a, b = engine.flat_param.float(), ref.flat_param.float()
     err = (a - b).abs().max().item()
     assert err < 2e-2, f"sharded and single-GPU parameters differ by {err}"

@@ -14,8 +14,8 @@ fp32 AdamW moments exist only for that slice.  A training step is
 2. per unit: reduce-scatter of the gradients over the shard group, then the allreduce of
    the owned slice over the replica groups (through the ``Manager``: averaged over the
    participating replicas, errors recorded instead of raised),
-3. ``Manager.should_commit()``; if it passes, fused AdamW on the owned slices and an
-   all-gather of the updated slices.
+3. ``Manager.should_commit()``; if it passes, fused AdamW on the owned slices; the updated
+   slices are all-gathered at the start of the next step.
 
 Steps 2 and 3 use the NVLink peer-memory kernels of ``torchft_b200.parallel.nvlink`` when a
 shard communicator is given; with a single GPU per replica group they reduce to the
@@ -191,7 +191,7 @@ class HSDPEngine:
         torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
 
     def optimizer_step(self, grad_scale: float = 1.0) -> None:
-        """Fused AdamW on the owned slices, then all-gather of the updated parameters."""
+        """Fused AdamW on the owned slices (the next step starts by all-gathering them)."""
         self.opt_step += 1
         b1, b2 = self.betas
         for u in self.units:
@@ -201,7 +201,6 @@ class HSDPEngine:
                 lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=self.weight_decay,
                 step=self.opt_step, grad_scale=grad_scale,
             )
-        self.gather_parameters()
 
     def gather_parameters(self) -> None:
         if self.comm.world > 1:
@@ -213,6 +212,11 @@ class HSDPEngine:
         """One fault-tolerant training step; returns the (local) loss tensor."""
         if self.manager is not None:
             self.manager.start_quorum()
+        # Updated slices are exchanged at the START of a step, on every rank, whether or not it (or a
+        # group mate) just recovered: recovery rewrites only the owned slice of a rank, and which
+        # ranks of a group recover differs per rank, so a collective inside load_state_dict would
+        # not be symmetric.
+        self.gather_parameters()
         self.zero_grad()
         loss = self.model(tokens, targets)
         loss.backward()
@@ -244,5 +248,3 @@ class HSDPEngine:
             put(self.exp_avg, sd["exp_avg"])  # type: ignore[arg-type]
             put(self.exp_avg_sq, sd["exp_avg_sq"])  # type: ignore[arg-type]
         self.opt_step = int(sd["opt_step"])  # type: ignore[arg-type]
-        # every rank of the group loads at the same point of the step, so a collective is safe here
-        self.gather_parameters()
