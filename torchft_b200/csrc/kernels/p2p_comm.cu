@@ -176,21 +176,41 @@ allreduce_kernel(Comm c, size_t off, long long nvec, float scale, int contribute
   const long long per = (nvec + c.world - 1) / c.world;
   const long long lo = per * c.rank;
   const long long hi = lo + per < nvec ? lo + per : nvec;
-  for (long long i = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < hi;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  // Each thread handles UNR vectors per round so that UNR * world loads are in flight per
+  // thread: NVLink round trips are microseconds, bandwidth comes from memory-level parallelism.
+  constexpr int UNR = 2;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < hi;
+       i0 += stride * UNR) {
+    uint4 in[UNR][MAX_RANKS];
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k >= c.world) break;
-      const int p = (c.rank + k) % c.world;  // start with the local copy, then walk the ring
-      if (mask & (1u << p)) Vec<T>::add(acc, ld_peer_v4(c.heap[p] + off + i * 16));
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        const int p = (c.rank + k) % c.world;  // start with the local copy, then walk the ring
+        in[u][k] = make_uint4(0, 0, 0, 0);
+        if (i < hi && (mask & (1u << p))) in[u][k] = ld_peer_v4(c.heap[p] + off + i * 16);
+      }
     }
-    const uint4 out = Vec<T>::pack(acc, scale);
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k >= c.world) break;
-      const int p = (c.rank + k) % c.world;
-      *reinterpret_cast<uint4*>(c.heap[p] + off + i * 16) = out;
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= hi) break;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        Vec<T>::add(acc, in[u][k]);
+      }
+      const uint4 out = Vec<T>::pack(acc, scale);
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        const int p = (c.rank + k) % c.world;
+        *reinterpret_cast<uint4*>(c.heap[p] + off + i * 16) = out;
+      }
     }
   }
   finish(c, flag);
