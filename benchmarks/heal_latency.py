@@ -1,7 +1,7 @@
 """Fault-injection benchmark: live-recovery (heal) latency, lost steps and steady throughput.
 
-    python benchmarks/heal_latency.py --transport nvlink --model llama_1b --steps 30 --kill-at 10
-    python benchmarks/heal_latency.py --transport http   --model llama_1b --steps 30 --kill-at 10
+    python benchmarks/heal_latency.py --transport nvlink --model llama_1b --steps 600 --kill-at 40
+    python benchmarks/heal_latency.py --transport http   --model llama_1b --steps 600 --kill-at 40
 
 Two replica groups of one GPU each train a Llama-shape model under per-step quorum.  After
 ``--kill-at`` committed steps replica 1 leaves (its process exits between two steps, with
@@ -165,10 +165,10 @@ def main() -> None:
     ap.add_argument("--lighthouse", default="")
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "http"])
     ap.add_argument("--model", default="llama_1b", choices=["llama3_8b", "llama_1b", "tiny"])
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--kill-at", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=600)
+    ap.add_argument("--kill-at", type=int, default=40)
     ap.add_argument("--timeout", type=float, default=300.0)
-    ap.add_argument("--device-timeout", type=float, default=5.0)
+    ap.add_argument("--device-timeout", type=float, default=30.0)
     ap.add_argument("--join-timeout-ms", type=int, default=200)
     ap.add_argument("--heartbeat-timeout-ms", type=int, default=1000)
     args = ap.parse_args()

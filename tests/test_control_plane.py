@@ -372,3 +372,28 @@ def test_wire_format_matches_protobuf_runtime():
 
     default = C.QuorumResult()
     assert default.replica_world_size == 1 and default.max_world_size == 1 and default.recover_src_rank is None
+
+
+def test_force_reconfigure_bumps_quorum_id_without_membership_change():
+    """A member whose step failed asks for a new quorum id; everybody gets it."""
+    lh = make_lighthouse(min_replicas=2, join_timeout_ms=5000)
+    managers = [make_manager(lh, f"fr_{i}") for i in range(2)]
+    try:
+        clients = [C.ManagerClient(m.address(), 5 * SEC) for m in managers]
+
+        def ask(i, step, force):
+            return clients[i].quorum(rank=0, step=step, checkpoint_metadata="", shrink_only=False, timeout=10 * SEC,
+                                     force_reconfigure=force)
+
+        with ThreadPoolExecutor(2) as ex:
+            a = [f.result() for f in [ex.submit(ask, i, 1, False) for i in range(2)]]
+            b = [f.result() for f in [ex.submit(ask, i, 2, False) for i in range(2)]]
+            c = [f.result() for f in [ex.submit(ask, i, 3, i == 1) for i in range(2)]]
+            d = [f.result() for f in [ex.submit(ask, i, 4, False) for i in range(2)]]
+        assert a[0].quorum_id == a[1].quorum_id == b[0].quorum_id == b[1].quorum_id
+        assert c[0].quorum_id == c[1].quorum_id == a[0].quorum_id + 1  # forced by replica 1 alone
+        assert d[0].quorum_id == c[0].quorum_id  # and stable again afterwards
+    finally:
+        for m in managers:
+            m.shutdown()
+        lh.shutdown()

@@ -80,6 +80,7 @@ wire::QuorumMember member_from_dict(const py::dict& d) {
   if (d.contains("step")) m.step = d["step"].cast<int64_t>();
   if (d.contains("world_size")) m.world_size = d["world_size"].cast<uint64_t>();
   if (d.contains("shrink_only")) m.shrink_only = d["shrink_only"].cast<bool>();
+  if (d.contains("force_reconfigure")) m.force_reconfigure = d["force_reconfigure"].cast<bool>();
   return m;
 }
 
@@ -159,11 +160,13 @@ PYBIND11_MODULE(TFT_MODULE_NAME, m) {
            py::arg("addr"), py::arg("connect_timeout"))
       .def("quorum",
            [](ManagerClient& c, int64_t rank, int64_t step, const std::string& checkpoint_metadata, bool shrink_only,
-              std::chrono::duration<double> timeout) {
-             return guarded([&] { return to_result(c.quorum(rank, step, checkpoint_metadata, shrink_only, to_ms(timeout))); });
+              std::chrono::duration<double> timeout, bool force_reconfigure) {
+             return guarded([&] {
+               return to_result(c.quorum(rank, step, checkpoint_metadata, shrink_only, to_ms(timeout), force_reconfigure));
+             });
            },
            py::arg("rank"), py::arg("step"), py::arg("checkpoint_metadata"), py::arg("shrink_only"),
-           py::arg("timeout"))
+           py::arg("timeout"), py::arg("force_reconfigure") = false)
       .def("checkpoint_metadata",
            [](ManagerClient& c, int64_t rank, std::chrono::duration<double> timeout) {
              return guarded([&] { return c.checkpoint_metadata(rank, to_ms(timeout)); });

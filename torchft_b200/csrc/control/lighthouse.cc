@@ -140,7 +140,9 @@ void Lighthouse::tick_locked() {
   if (!result.first) return;
   std::vector<wire::QuorumMember>& members = *result.first;
   // The id only moves when the ordered set of replica ids changes.
-  if (!state_.prev_quorum || quorum_changed(members, state_.prev_quorum->participants)) {
+  bool forced = false;
+  for (const auto& m : members) forced = forced || m.force_reconfigure;
+  if (!state_.prev_quorum || forced || quorum_changed(members, state_.prev_quorum->participants)) {
     state_.quorum_id += 1;
     net::log_info("torchft_b200::lighthouse",
                   "Detected quorum change, bumping quorum_id to " + std::to_string(state_.quorum_id));

@@ -21,12 +21,13 @@ void LighthouseClient::heartbeat(const std::string& replica_id, net::Millis time
 }
 
 wire::ManagerQuorumResponse ManagerClient::quorum(int64_t rank, int64_t step, const std::string& checkpoint_metadata,
-                                                  bool shrink_only, net::Millis timeout) {
+                                                  bool shrink_only, net::Millis timeout, bool force_reconfigure) {
   wire::ManagerQuorumRequest req;
   req.rank = rank;
   req.step = step;
   req.checkpoint_metadata = checkpoint_metadata;
   req.shrink_only = shrink_only;
+  req.force_reconfigure = force_reconfigure;
   std::string resp = client_.call("/torchft.ManagerService/Quorum", req.encode(), timeout);
   return wire::ManagerQuorumResponse::decode(resp);
 }
@@ -131,6 +132,7 @@ net::Status ManagerServer::handle_quorum(const net::CallContext& ctx, const std:
   std::unique_lock<std::mutex> lk(mu_);
   checkpoint_metadata_[rank] = request.checkpoint_metadata;
   participants_.insert(rank);
+  round_force_reconfigure_ = round_force_reconfigure_ || request.force_reconfigure;
   const uint64_t my_seq = quorum_seq_;
 
   if (participants_.size() >= world_size_ && !quorum_in_flight_) {
@@ -144,6 +146,8 @@ net::Status ManagerServer::handle_quorum(const net::CallContext& ctx, const std:
     me.step = request.step;
     me.world_size = world_size_;
     me.shrink_only = request.shrink_only;
+    me.force_reconfigure = round_force_reconfigure_;
+    round_force_reconfigure_ = false;
     lk.unlock();
     net::Status st;
     wire::Quorum q;

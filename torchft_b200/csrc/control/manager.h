@@ -35,7 +35,7 @@ class ManagerClient {
  public:
   ManagerClient(const std::string& addr, net::Millis connect_timeout) : client_(addr, connect_timeout) {}
   wire::ManagerQuorumResponse quorum(int64_t rank, int64_t step, const std::string& checkpoint_metadata,
-                                     bool shrink_only, net::Millis timeout);
+                                     bool shrink_only, net::Millis timeout, bool force_reconfigure = false);
   std::string checkpoint_metadata(int64_t rank, net::Millis timeout);
   bool should_commit(int64_t rank, int64_t step, bool should_commit, net::Millis timeout);
   void kill(const std::string& msg, net::Millis timeout);
@@ -77,6 +77,7 @@ class ManagerServer {
   // quorum round state
   std::map<int64_t, std::string> checkpoint_metadata_;
   std::set<int64_t> participants_;
+  bool round_force_reconfigure_ = false;  // OR over the ranks of the current round
   uint64_t quorum_seq_ = 0;            // bumped whenever a round resolves
   bool quorum_in_flight_ = false;
   wire::Quorum last_quorum_;

@@ -95,6 +95,7 @@ std::string QuorumMember::encode() const {
   w.put_int64(4, step);
   w.put_uint64(5, world_size);
   w.put_bool(6, shrink_only);
+  w.put_bool(7, force_reconfigure);
   return w.take();
 }
 QuorumMember QuorumMember::decode(const std::string& s) {
@@ -108,6 +109,7 @@ QuorumMember QuorumMember::decode(const std::string& s) {
     else if (f == 4 && wt == kVarint) m.step = static_cast<int64_t>(r.varint());
     else if (f == 5 && wt == kVarint) m.world_size = r.varint();
     else if (f == 6 && wt == kVarint) m.shrink_only = r.varint() != 0;
+    else if (f == 7 && wt == kVarint) m.force_reconfigure = r.varint() != 0;
     else r.skip(wt);
   }
   return m;
@@ -201,6 +203,7 @@ std::string ManagerQuorumRequest::encode() const {
   w.put_int64(2, step);
   w.put_string(3, checkpoint_metadata);
   w.put_bool(4, shrink_only);
+  w.put_bool(5, force_reconfigure);
   return w.take();
 }
 ManagerQuorumRequest ManagerQuorumRequest::decode(const std::string& s) {
@@ -212,6 +215,7 @@ ManagerQuorumRequest ManagerQuorumRequest::decode(const std::string& s) {
     else if (f == 2 && wt == kVarint) m.step = static_cast<int64_t>(r.varint());
     else if (f == 3 && wt == kLen) m.checkpoint_metadata = r.bytes();
     else if (f == 4 && wt == kVarint) m.shrink_only = r.varint() != 0;
+    else if (f == 5 && wt == kVarint) m.force_reconfigure = r.varint() != 0;
     else r.skip(wt);
   }
   return m;

@@ -55,6 +55,9 @@ struct QuorumMember {
   int64_t step = 0;
   uint64_t world_size = 0;
   bool shrink_only = false;
+  // Extension (field 7): a member whose previous step failed asks for a fresh quorum id so that
+  // every member re-creates its communicator even though membership did not change.
+  bool force_reconfigure = false;
   std::string encode() const;
   static QuorumMember decode(const std::string& s);
 };
@@ -95,6 +98,7 @@ struct ManagerQuorumRequest {
   int64_t step = 0;
   std::string checkpoint_metadata;
   bool shrink_only = false;
+  bool force_reconfigure = false;  // extension, field 5
   std::string encode() const;
   static ManagerQuorumRequest decode(const std::string& s);
 };

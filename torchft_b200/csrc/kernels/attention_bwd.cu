@@ -78,15 +78,18 @@ __device__ __forceinline__ void store_acc(uint32_t taddr, __nv_bfloat16* dst, fl
 }
 
 // ------------------------------------------------------------------ dK, dV
+// Q and dO tiles are double buffered.  P and dS share ONE operand buffer: P is written first
+// and consumed by the dV MMAs, then dS (kept in registers meanwhile) overwrites it for the dK
+// MMAs.  That is what makes room for the second Q/dO stage.
 template <int HD>
 struct DkvSmem {
   static constexpr uint32_t TILE = BLK * HD * 2;
-  static constexpr uint32_t K = 0, V = TILE, Q = 2 * TILE, DO = 3 * TILE;
-  static constexpr uint32_t P = 4 * TILE, DS = P + BLK * BLK * 2;
-  static constexpr uint32_t BARS = DS + BLK * BLK * 2;
+  static constexpr uint32_t K = 0, V = TILE, Q = 2 * TILE /*2 stages*/, DO = 4 * TILE /*2 stages*/;
+  static constexpr uint32_t PDS = 6 * TILE;
+  static constexpr uint32_t BARS = PDS + BLK * BLK * 2;
   static constexpr uint32_t TOTAL = BARS + 256 + 1024;
 };
-enum DkvBar { KV_FULL = 0, Q_FULL, DO_FULL, Q_EMPTY, DO_EMPTY, SDP_FULL, PDS_READY, PDS_EMPTY, ACC_DONE, NUM_DKV_BARS };
+enum DkvBar { KV_FULL = 0, Q_FULL0, Q_FULL1, DO_FULL0, DO_FULL1, Q_EMPTY0, Q_EMPTY1, DO_EMPTY0, DO_EMPTY1, SDP_FULL, P_READY, P_FREE, DS_READY, DS_FREE, ACC_DONE, NUM_DKV_BARS };
 
 template <int HD>
 __global__ void __launch_bounds__(320, 1)
@@ -116,7 +119,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   const int n_items = G * per_head;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_DKV_BARS; ++i) mbar_init(bar(i), i == PDS_READY ? 256 : 1);
+    for (int i = 0; i < NUM_DKV_BARS; ++i) mbar_init(bar(i), (i == P_READY || i == DS_READY) ? 256 : 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq);
@@ -142,43 +145,58 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       for (int t = 0; t < n_items; ++t) {
         const int head = kv_head * G + t / per_head;
         const int it = jt + t % per_head;
-        if (!mbar_wait(bar(Q_EMPTY), (t & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(bar(Q_FULL), L::TILE);
-        load_tile<HD>(base + L::Q, &tq, bar(Q_FULL), head, it * BLK, batch);
-        if (!mbar_wait(bar(DO_EMPTY), (t & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(bar(DO_FULL), L::TILE);
-        load_tile<HD>(base + L::DO, &tdo, bar(DO_FULL), head, it * BLK, batch);
+        const int st = t & 1;
+        const uint32_t free_parity = ((t >> 1) & 1) ^ 1;
+        if (!mbar_wait(bar(Q_EMPTY0 + st), free_parity, abort_flag)) break;
+        mbar_expect_tx(bar(Q_FULL0 + st), L::TILE);
+        load_tile<HD>(base + L::Q + st * L::TILE, &tq, bar(Q_FULL0 + st), head, it * BLK, batch);
+        if (!mbar_wait(bar(DO_EMPTY0 + st), free_parity, abort_flag)) break;
+        mbar_expect_tx(bar(DO_FULL0 + st), L::TILE);
+        load_tile<HD>(base + L::DO + st * L::TILE, &tdo, bar(DO_FULL0 + st), head, it * BLK, batch);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
       constexpr uint32_t idesc_g = make_idesc_bf16(BLK, HD, true, true);
-      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
-      for (int t = 0; t < n_items && ok; ++t) {
-        const uint32_t ph = t & 1;
-        if (!mbar_wait(bar(Q_FULL), ph, abort_flag) || !mbar_wait(bar(DO_FULL), ph, abort_flag)) { ok = false; break; }
+      // S = Q K^T and dP = dO V^T of item t (its Q/dO stage must have landed)
+      auto issue_sdp = [&](int t) -> bool {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(bar(Q_FULL0 + st), ph, abort_flag) || !mbar_wait(bar(DO_FULL0 + st), ph, abort_flag)) return false;
         tc_fence_after();
+        const uint32_t sq = base + L::Q + st * L::TILE, sdo = base + L::DO + st * L::TILE;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_bf16(t_s, kmajor_desc(base + L::Q, k), kmajor_desc(base + L::K, k), idesc_s, k != 0);
+        for (int k = 0; k < HD / 16; ++k) umma_bf16(t_s, kmajor_desc(sq, k), kmajor_desc(base + L::K, k), idesc_s, k != 0);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_bf16(t_dp, kmajor_desc(base + L::DO, k), kmajor_desc(base + L::V, k), idesc_s, k != 0);
+        for (int k = 0; k < HD / 16; ++k) umma_bf16(t_dp, kmajor_desc(sdo, k), kmajor_desc(base + L::V, k), idesc_s, k != 0);
         umma_commit(bar(SDP_FULL));
-        if (!mbar_wait(bar(PDS_READY), ph, abort_flag)) { ok = false; break; }
+        return true;
+      };
+      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
+      if (ok && n_items > 0) ok = issue_sdp(0);
+      for (int t = 0; t < n_items && ok; ++t) {
+        const int st = t & 1;
+        const uint32_t sq = base + L::Q + st * L::TILE, sdo = base + L::DO + st * L::TILE;
+        // P_READY also means: the softmax threads are done reading S and dP of item t
+        if (!mbar_wait(bar(P_READY), t & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         // dV += P^T dO   (contraction over the 128 query rows)
 #pragma unroll
         for (int k = 0; k < BLK / 16; ++k)
-          umma_bf16(t_dv, mnmajor_desc(base + L::P, k), mnmajor_desc(base + L::DO, k), idesc_g, (t | k) != 0);
-        umma_commit(bar(DO_EMPTY));
+          umma_bf16(t_dv, mnmajor_desc(base + L::PDS, k), mnmajor_desc(sdo, k), idesc_g, (t | k) != 0);
+        umma_commit(bar(DO_EMPTY0 + st));
+        umma_commit(bar(P_FREE));
+        // scores of the NEXT item run while the softmax threads finish dS of this one
+        if (t + 1 < n_items && !issue_sdp(t + 1)) { ok = false; break; }
+        if (!mbar_wait(bar(DS_READY), t & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
         // dK += dS^T Q
 #pragma unroll
         for (int k = 0; k < BLK / 16; ++k)
-          umma_bf16(t_dk, mnmajor_desc(base + L::DS, k), mnmajor_desc(base + L::Q, k), idesc_g, (t | k) != 0);
-        umma_commit(bar(Q_EMPTY));
-        umma_commit(bar(PDS_EMPTY));
+          umma_bf16(t_dk, mnmajor_desc(base + L::PDS, k), mnmajor_desc(sq, k), idesc_g, (t | k) != 0);
+        umma_commit(bar(Q_EMPTY0 + st));
+        umma_commit(bar(DS_FREE));
       }
       if (ok) umma_commit(bar(ACC_DONE));
     }
@@ -198,27 +216,36 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const float dl = row_ok ? delta[stat] : 0.f;
       if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      if (t > 0 && !mbar_wait(bar(PDS_EMPTY), (t - 1) & 1, abort_flag)) { ok = false; break; }
       const bool diag = (it == jt);
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
+      float p[2][32], ds[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
         tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
         tmem_ld_wait();
-        float p[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const bool keep = row_ok && (!diag || (c * 32 + i) <= r);
-          p[i] = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
-          ds[i] = p[i] * (__uint_as_float(dv[i]) - dl);
+          p[cc][i] = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
+          ds[cc][i] = p[cc][i] * (__uint_as_float(dv[i]) - dl);
         }
-        store_row_chunk(smem + L::P, r, c, p);
-        store_row_chunk(smem + L::DS, r, c, ds);
       }
+      // the operand buffer is free once the dK MMAs of the previous item have read dS from it
+      if (t > 0 && !mbar_wait(bar(DS_FREE), (t - 1) & 1, abort_flag)) { ok = false; break; }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) store_row_chunk(smem + L::PDS, r, half * 2 + cc, p[cc]);
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(bar(PDS_READY));
+      mbar_arrive(bar(P_READY));
+      // ... and dS may replace P once the dV MMAs have read it
+      if (!mbar_wait(bar(P_FREE), t & 1, abort_flag)) { ok = false; break; }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) store_row_chunk(smem + L::PDS, r, half * 2 + cc, ds[cc]);
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar(DS_READY));
     }
     if (ok && mbar_wait(bar(ACC_DONE), 0, abort_flag)) {
       tc_fence_after();
@@ -244,15 +271,17 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 }
 
 // ------------------------------------------------------------------ dQ
+// K tiles are double buffered, V (needed only for dP, early in an iteration) has one stage,
+// and dS has two buffers so that the softmax of tile j+1 overlaps the dQ MMAs of tile j.
 template <int HD>
 struct DqSmem {
   static constexpr uint32_t TILE = BLK * HD * 2;
-  static constexpr uint32_t Q = 0, DO = TILE, K = 2 * TILE /*2 stages*/, V = 4 * TILE /*2 stages*/;
-  static constexpr uint32_t DS = 6 * TILE;
-  static constexpr uint32_t BARS = DS + BLK * BLK * 2;
+  static constexpr uint32_t Q = 0, DO = TILE, K = 2 * TILE /*2 stages*/, V = 4 * TILE /*1 stage*/;
+  static constexpr uint32_t DS = 5 * TILE;  // 2 buffers of [128 x 128] bf16
+  static constexpr uint32_t BARS = DS + 2 * BLK * BLK * 2;
   static constexpr uint32_t TOTAL = BARS + 256 + 1024;
 };
-enum DqBar { QDO_FULL = 0, DQ_K_FULL0, DQ_K_FULL1, DQ_V_FULL0, DQ_V_FULL1, DQ_KV_EMPTY0, DQ_KV_EMPTY1, DQ_SDP_FULL, DS_READY, DS_EMPTY, DQ_DONE, NUM_DQ_BARS };
+enum DqBar { QDO_FULL = 0, DQ_K_FULL0, DQ_K_FULL1, DQ_V_FULL, DQ_K_EMPTY0, DQ_K_EMPTY1, DQ_V_EMPTY, DQ_SDP_FULL, DQ_DS_READY0, DQ_DS_READY1, DQ_DS_FREE0, DQ_DS_FREE1, DQ_DONE, NUM_DQ_BARS };
 
 template <int HD>
 __global__ void __launch_bounds__(320, 1)
@@ -278,7 +307,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
   const int n_kv = qt + 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_DQ_BARS; ++i) mbar_init(bar(i), i == DS_READY ? 256 : 1);
+    for (int i = 0; i < NUM_DQ_BARS; ++i) mbar_init(bar(i), (i == DQ_DS_READY0 || i == DQ_DS_READY1) ? 256 : 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq);
@@ -303,39 +332,46 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
       load_tile<HD>(base + L::DO, &tdo, bar(QDO_FULL), head, qt * BLK, batch);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
-        if (!mbar_wait(bar(DQ_KV_EMPTY0 + st), ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        if (!mbar_wait(bar(DQ_K_EMPTY0 + st), ((j >> 1) & 1) ^ 1, abort_flag)) break;
         mbar_expect_tx(bar(DQ_K_FULL0 + st), L::TILE);
         load_tile<HD>(base + L::K + st * L::TILE, &tk, bar(DQ_K_FULL0 + st), kv_head, j * BLK, batch);
-        mbar_expect_tx(bar(DQ_V_FULL0 + st), L::TILE);
-        load_tile<HD>(base + L::V + st * L::TILE, &tv, bar(DQ_V_FULL0 + st), kv_head, j * BLK, batch);
+        if (!mbar_wait(bar(DQ_V_EMPTY), (j & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(DQ_V_FULL), L::TILE);
+        load_tile<HD>(base + L::V, &tv, bar(DQ_V_FULL), kv_head, j * BLK, batch);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BLK, BLK, false, false);
       constexpr uint32_t idesc_q = make_idesc_bf16(BLK, HD, false, true);
+      auto issue_sdp = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(bar(DQ_K_FULL0 + st), (j >> 1) & 1, abort_flag) || !mbar_wait(bar(DQ_V_FULL), j & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t sk = base + L::K + st * L::TILE;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_bf16(t_s, kmajor_desc(base + L::Q, k), kmajor_desc(sk, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_bf16(t_dp, kmajor_desc(base + L::DO, k), kmajor_desc(base + L::V, k), idesc_s, k != 0);
+        umma_commit(bar(DQ_SDP_FULL));
+        umma_commit(bar(DQ_V_EMPTY));
+        return true;
+      };
       bool ok = mbar_wait(bar(QDO_FULL), 0, abort_flag);
+      if (ok) ok = issue_sdp(0);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar(DQ_K_FULL0 + st), ph, abort_flag) || !mbar_wait(bar(DQ_V_FULL0 + st), ph, abort_flag)) { ok = false; break; }
+        // dS of tile j is in shared memory, and S / dP of tile j have been read
+        if (!mbar_wait(bar(DQ_DS_READY0 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sk = base + L::K + st * L::TILE, sv = base + L::V + st * L::TILE;
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_bf16(t_s, kmajor_desc(base + L::Q, k), kmajor_desc(sk, k), idesc_s, k != 0);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_bf16(t_dp, kmajor_desc(base + L::DO, k), kmajor_desc(sv, k), idesc_s, k != 0);
-        umma_commit(bar(DQ_SDP_FULL));
-        if (!mbar_wait(bar(DS_READY), j & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
+        // scores of the next tile first, so its softmax overlaps the dQ MMAs below
+        if (j + 1 < n_kv && !issue_sdp(j + 1)) { ok = false; break; }
         // dQ += dS K_j   (contraction over the 128 key rows)
+        const uint32_t sk = base + L::K + st * L::TILE, sds = base + L::DS + st * (BLK * BLK * 2);
 #pragma unroll
-        for (int k = 0; k < BLK / 16; ++k)
-          umma_bf16(t_dq, kmajor_desc(base + L::DS, k), mnmajor_desc(sk, k), idesc_q, (j | k) != 0);
-        umma_commit(bar(DQ_KV_EMPTY0 + st));
-        umma_commit(bar(DS_EMPTY));
+        for (int k = 0; k < BLK / 16; ++k) umma_bf16(t_dq, kmajor_desc(sds, k), mnmajor_desc(sk, k), idesc_q, (j | k) != 0);
+        umma_commit(bar(DQ_K_EMPTY0 + st));
+        umma_commit(bar(DQ_DS_FREE0 + st));
       }
       if (ok) umma_commit(bar(DQ_DONE));
     }
@@ -351,28 +387,33 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
     const float dl = row_ok ? delta[stat] : 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
       if (!mbar_wait(bar(DQ_SDP_FULL), j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      if (j > 0 && !mbar_wait(bar(DS_EMPTY), (j - 1) & 1, abort_flag)) { ok = false; break; }
       const bool diag = (j == qt);
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
+      float ds[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
         tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
         tmem_ld_wait();
-        float ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const bool keep = row_ok && (!diag || (c * 32 + i) <= r);
           const float p = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
-          ds[i] = p * (__uint_as_float(dv[i]) - dl);
+          ds[cc][i] = p * (__uint_as_float(dv[i]) - dl);
         }
-        store_row_chunk(smem + L::DS, r, c, ds);
       }
+      // this dS buffer was last read by the dQ MMAs of tile j-2
+      if (!mbar_wait(bar(DQ_DS_FREE0 + st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+      uint8_t* dst = smem + L::DS + st * (BLK * BLK * 2);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) store_row_chunk(dst, r, half * 2 + cc, ds[cc]);
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(bar(DS_READY));
+      mbar_arrive(bar(DQ_DS_READY0 + st));
     }
     if (ok && mbar_wait(bar(DQ_DONE), 0, abort_flag)) {
       tc_fence_after();

@@ -258,6 +258,10 @@ class Manager:
         """
         if self._quorum_future is not None:
             self._quorum_future.result()
+        # A failed step can leave the communicator out of step with its peers (one side gave up
+        # on a collective the other side never started).  Ask for a fresh quorum id: every member
+        # then reconfigures even though the membership is unchanged.
+        force_reconfigure = self._errored is not None
         self._errored = None
         self._healing = False
         self._quorum_future = self._executor.submit(
@@ -265,6 +269,7 @@ class Manager:
             allow_heal=allow_heal,
             shrink_only=shrink_only,
             quorum_timeout=timeout or self._quorum_timeout,
+            force_reconfigure=force_reconfigure,
         )
         if not self._use_async_quorum:
             self.wait_quorum()
@@ -278,14 +283,18 @@ class Manager:
         assert self._quorum_future is not None, "must call start_quorum before wait_quorum"
         self._quorum_future.result()
 
-    def _async_quorum(self, allow_heal: bool, shrink_only: bool, quorum_timeout: timedelta) -> None:
+    def _async_quorum(
+        self, allow_heal: bool, shrink_only: bool, quorum_timeout: timedelta, force_reconfigure: bool = False
+    ) -> None:
         with trace_range("tft.quorum"):
+            kwargs = {"force_reconfigure": True} if force_reconfigure else {}
             quorum = self._client.quorum(
                 rank=self._rank,
                 step=self._step,
                 checkpoint_metadata=self._checkpoint_transport.metadata(),
                 shrink_only=shrink_only,
                 timeout=quorum_timeout,
+                **kwargs,
             )
         max_step = quorum.max_step
         self._replica_rank = quorum.replica_rank
