@@ -206,30 +206,53 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     const int r = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     bool ok = true;
+    float next_lse = 0.f, next_dl = 0.f;
+    if (n_items > 0) {
+      const int row0 = jt * BLK + r;
+      const long long stat0 = (static_cast<long long>(batch) * Hq + kv_head * G) * S + row0;
+      next_lse = row0 < S ? LSE[stat0] : 0.f;
+      next_dl = row0 < S ? delta[stat0] : 0.f;
+    }
     for (int t = 0; t < n_items; ++t) {
-      const int head = kv_head * G + t / per_head;
       const int it = jt + t % per_head;
       const int row = it * BLK + r;
       const bool row_ok = row < S;
-      const long long stat = (static_cast<long long>(batch) * Hq + head) * S + row;
-      const float lse = row_ok ? LSE[stat] : 0.f;
-      const float dl = row_ok ? delta[stat] : 0.f;
+      const float lse = next_lse, dl = next_dl;
+      if (t + 1 < n_items) {  // statistics of the next item travel while this one is processed
+        const int nhead = kv_head * G + (t + 1) / per_head;
+        const int nrow = (jt + (t + 1) % per_head) * BLK + r;
+        const long long nstat = (static_cast<long long>(batch) * Hq + nhead) * S + nrow;
+        next_lse = nrow < S ? LSE[nstat] : 0.f;
+        next_dl = nrow < S ? delta[nstat] : 0.f;
+      }
       if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = (it == jt);
       float p[2][32], ds[2][32];
+      // all four tensor-memory loads are issued before the single wait, so their latencies overlap
+      uint32_t sv[2][32], dv[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld_32x32(t_s + lane_addr + (half * 2 + cc) * 32, sv[cc]);
+        tmem_ld_32x32(t_dp + lane_addr + (half * 2 + cc) * 32, dv[cc]);
+      }
+      tmem_ld_wait();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
-        tmem_ld_wait();
+        if (diag || !row_ok) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool keep = row_ok && (!diag || (c * 32 + i) <= r);
-          p[cc][i] = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
-          ds[cc][i] = p[cc][i] * (__uint_as_float(dv[i]) - dl);
+          for (int i = 0; i < 32; ++i) {
+            const bool keep = row_ok && (c * 32 + i) <= r;
+            p[cc][i] = keep ? fast_exp2(__uint_as_float(sv[cc][i]) * scale_log2 - lse) : 0.f;
+            ds[cc][i] = p[cc][i] * (__uint_as_float(dv[cc][i]) - dl);
+          }
+        } else {  // mask-free fast path: every tile off the diagonal
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            p[cc][i] = fast_exp2(__uint_as_float(sv[cc][i]) * scale_log2 - lse);
+            ds[cc][i] = p[cc][i] * (__uint_as_float(dv[cc][i]) - dl);
+          }
         }
       }
       // the operand buffer is free once the dK MMAs of the previous item have read dS from it
@@ -392,18 +415,29 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ C
       tc_fence_after();
       const bool diag = (j == qt);
       float ds[2][32];
+      uint32_t sv[2][32], dv[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld_32x32(t_s + lane_addr + (half * 2 + cc) * 32, sv[cc]);
+        tmem_ld_32x32(t_dp + lane_addr + (half * 2 + cc) * 32, dv[cc]);
+      }
+      tmem_ld_wait();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
-        tmem_ld_wait();
+        if (diag || !row_ok) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool keep = row_ok && (!diag || (c * 32 + i) <= r);
-          const float p = keep ? fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse) : 0.f;
-          ds[cc][i] = p * (__uint_as_float(dv[i]) - dl);
+          for (int i = 0; i < 32; ++i) {
+            const bool keep = row_ok && (c * 32 + i) <= r;
+            const float p = keep ? fast_exp2(__uint_as_float(sv[cc][i]) * scale_log2 - lse) : 0.f;
+            ds[cc][i] = p * (__uint_as_float(dv[cc][i]) - dl);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float p = fast_exp2(__uint_as_float(sv[cc][i]) * scale_log2 - lse);
+            ds[cc][i] = p * (__uint_as_float(dv[cc][i]) - dl);
+          }
         }
       }
       // this dS buffer was last read by the dQ MMAs of tile j-2
