@@ -1,9 +1,13 @@
 """Reference arm of ``bench.py``: the reference's own stack on the same metric and config.
 
 The reference (torchft 0.1.1) ships its control plane as a Rust extension built with
-maturin; neither maturin nor a Rust toolchain is available offline, so
-``pip install --no-index ... /root/reference`` stops at the build backend.  Until an
-install exists under ``baseline/_ref`` this arm reports itself unavailable.
+maturin; neither maturin nor a Rust toolchain is available offline, so a pip install of the
+reference stops at the build backend.  ``baseline/make_ref.py`` therefore lays the reference's
+unmodified Python sources under ``baseline/_ref/torchft`` next to this repository's C++ control
+plane compiled under the reference's extension name (``torchft.torchft``, same classes and
+signatures).  ``baseline/reference_runner.py`` then drives the reference's Manager, DDP wrapper,
+optimizer wrapper and NCCL process group.  Without that directory the arm reports itself
+unavailable.
 """
 
 from __future__ import annotations
@@ -18,7 +22,7 @@ def run_reference(args) -> None:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({
                 "impl": "reference",
-                "unavailable": "reference not installable offline: build backend maturin and the Rust toolchain (cargo, rustc, protoc) are missing",
+                "unavailable": "reference not installed: run baseline/make_ref.py (the Rust extension needs maturin, cargo and protoc, which are missing offline)",
             }), flush=True)
         return
     from baseline.reference_runner import run  # populated only when an install exists

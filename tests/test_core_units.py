@@ -92,6 +92,23 @@ def test_checkpoint_server_round_trip_and_gate():
         server.shutdown()
 
 
+def test_checkpoint_server_serves_views_of_one_arena():
+    """State kept as bf16 and fp32 views of ONE byte buffer (a heap) is sent tensor by tensor."""
+    arena = torch.zeros(1 << 16, dtype=torch.uint8)
+    a = arena[:1024].view(torch.bfloat16)
+    b = arena[4096 : 4096 + 4096].view(torch.float32)
+    a.copy_(torch.arange(512).to(torch.bfloat16))
+    b.copy_(torch.arange(1024).float())
+    server = CheckpointServer(timeout=timedelta(seconds=10))
+    try:
+        server.send_checkpoint([], 3, {"p": [a], "m": b}, timedelta(seconds=10))
+        out = server.recv_checkpoint(0, server.metadata(), 3, timedelta(seconds=10))
+        assert torch.equal(out["p"][0], a) and torch.equal(out["m"], b)
+        assert out["m"].untyped_storage().nbytes() == b.numel() * 4  # not the whole arena
+    finally:
+        server.shutdown()
+
+
 def test_checkpoint_server_gate_blocks_until_allowed():
     server = CheckpointServer(timeout=timedelta(seconds=10))
     try:

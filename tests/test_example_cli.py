@@ -66,3 +66,45 @@ def test_standalone_lighthouse_binary_usage():
         build.build_control()
     res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=30)
     assert res.returncode == 2 and "min_replicas is required" in res.stderr
+
+
+def test_job_description_roles():
+    from torchft_b200 import torchx as tx
+
+    app = tx.hsdp("--flag", replicas=3, workers_per_replica=2, max_restarts=4, env={"FOO": "1"})
+    assert app.name == "torchft" and [r.name for r in app.roles] == ["replica_0", "replica_1", "replica_2"]
+    for g, role in enumerate(app.roles):
+        assert role.entrypoint == "torchrun" and role.num_replicas == 2
+        assert f"--master_port={29600 + g}" in role.args and "--nproc_per_node=2" in role.args
+        assert "--max_restarts=4" in role.args and role.args[-2:] == ["train_ddp.py", "--flag"]
+        assert role.env["REPLICA_GROUP_ID"] == str(g) and role.env["NUM_REPLICA_GROUPS"] == "3"
+        assert role.env["FOO"] == "1" and role.env["CUDA_VISIBLE_DEVICES"] == ""
+        assert role.env["TORCHFT_LIGHTHOUSE"].startswith("http://")
+    import pytest
+
+    with pytest.raises(ValueError):
+        tx.hsdp(replicas=0)
+
+
+def test_local_launcher_runs_two_replica_groups(tmp_path):
+    """torchrun per replica group, started from the job description; the groups find each other through the lighthouse."""
+    from torchft_b200 import _control
+    from torchft_b200 import torchx as tx
+
+    lighthouse = _control.Lighthouse(bind="[::]:0", min_replicas=2, join_timeout_ms=20000)
+    try:
+        port = lighthouse.address().rsplit(":", 1)[1]
+        app = tx.hsdp(replicas=2, workers_per_replica=1, max_restarts=0, script=os.path.join(ROOT, "train_ddp.py"),
+                      env={"TORCHFT_LIGHTHOUSE": f"http://127.0.0.1:{port}", "TOTAL_STEPS": "4", "PYTHONPATH": ROOT,
+                           "TORCHFT_B200_LOG": "", "LOGLEVEL": "WARNING", "TORCH_CPP_LOG_LEVEL": "WARNING"})
+        for role in app.roles:  # the default ports may be taken on a shared host
+            role.args[0] = f"--master_port={_free_port()}"
+        run = tx.run_local(app, log_dir=str(tmp_path))
+        try:
+            codes = run.wait(timeout=300)
+        finally:
+            run.stop()
+        logs = "\n".join(open(os.path.join(tmp_path, f)).read()[-2000:] for f in os.listdir(tmp_path))
+        assert codes == {"replica_0": 0, "replica_1": 0}, logs
+    finally:
+        lighthouse.shutdown()

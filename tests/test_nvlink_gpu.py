@@ -299,3 +299,43 @@ def test_two_replicas_quorum_heal_and_allreduce_on_gpus():
     pulled = _spawn(_replicas_with_manager, 2)
     # exactly one of the two replicas healed from the other at step 0, GPU to GPU
     assert sorted(p > 0 for p in pulled) == [False, True]
+
+
+def _ag_gemm(rank, world, port):
+    """All-gather fused into the GEMM against an fp32 reference of the same product."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, SymmetricHeap
+
+    store = PrefixStore("agg", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False))
+    heap = SymmetricHeap.get(512 << 20)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=20))
+    comm.configure(store, rank, world, "epoch-ag")
+    for (M, N, K, copy_ctas) in ((256, 256 * world, 128, 2), (1000, 512 * world, 1024, 16), (4096, 1024 * world, 2048, 8)):
+        w_all = torch.randn(N, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).to(torch.bfloat16)
+        x = torch.randn(M, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(9 + rank)).to(torch.bfloat16)
+        w = heap.alloc(N * K, torch.bfloat16).view(N, K)
+        rows = N // world
+        for rep in range(2):  # twice: the second call starts from a gathered buffer that is reset first
+            w.fill_(float("nan"))
+            w[rank * rows : (rank + 1) * rows].copy_(w_all[rank * rows : (rank + 1) * rows])
+            comm.barrier()  # nobody pulls before every rank wrote its rows
+            y = comm.all_gather_linear(x, w, copy_ctas=copy_ctas)
+            torch.cuda.synchronize()
+            comm.check()
+            assert torch.equal(w, w_all), "gathered weight differs"
+            ref = x.float() @ w_all.float().t()
+            err = (y.float() - ref).abs().max().item()
+            assert err <= 0.02 * ref.abs().max().item() + 1e-2, (M, N, K, rep, err)
+            comm.barrier()  # nobody resets its rows while a peer may still read them
+    return "ok"
+
+
+def test_all_gather_fused_gemm_two_gpus():
+    _need_gpus(2)
+    _spawn(_ag_gemm, 2)
+
+
+def test_all_gather_fused_gemm_four_gpus():
+    _need_gpus(4)
+    _spawn(_ag_gemm, 4)

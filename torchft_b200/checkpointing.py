@@ -36,6 +36,29 @@ logger: logging.Logger = logging.getLogger(__name__)
 T = TypeVar("T")
 
 
+def _compact(state: object) -> object:
+    """Tensors of a state dict as stand-alone CPU tensors.
+
+    ``torch.save`` writes the whole storage behind every tensor and refuses storages that are
+    viewed under two dtypes.  State that lives as views of one large arena (a symmetric heap, a
+    flat parameter buffer) would therefore be saved with the entire arena, or not at all; a
+    copy to host memory gives every tensor a storage of exactly its own size.
+    """
+    from torch.utils._pytree import tree_map
+
+    def one(x: object) -> object:
+        if not isinstance(x, torch.Tensor):
+            return x
+        t = x.detach()
+        if t.device.type != "cpu":
+            return t.to("cpu")
+        if t.untyped_storage().nbytes() != t.numel() * t.element_size():
+            return t.clone()
+        return t
+
+    return tree_map(one, state)
+
+
 class CheckpointTransport(Generic[T], ABC):
     @abstractmethod
     def metadata(self) -> str:
@@ -100,7 +123,7 @@ class CheckpointServer(CheckpointTransport[T]):
                         self.send_response(200)
                         self.send_header("Content-type", "application/octet-stream")
                         self.end_headers()
-                        torch.save(transport._state_dict, self.wfile)
+                        torch.save(_compact(transport._state_dict), self.wfile)
                 except Exception as e:  # noqa: BLE001 - reported to the client
                     logger.exception(f"exception while serving checkpoint: {e}")
                     try:

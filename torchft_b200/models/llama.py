@@ -153,6 +153,10 @@ class Llama(nn.Module):
         # gradients of that unit are final; an engine uses it to start communicating them
         # while the rest of the backward pass still runs.
         self.unit_grad_ready = None
+        # Called in forward with a unit name right before the first kernel that reads that
+        # unit's parameters; an engine that refreshes parameters on another stream makes the
+        # current stream wait for the unit's refresh here.
+        self.unit_pre_forward = None
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0) -> None:
@@ -181,10 +185,15 @@ class Llama(nn.Module):
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``tokens [B, S]`` -> mean cross entropy against ``targets`` (or bf16 logits without targets)."""
         cs = self.rope_cache(tokens.device)
+        pre = self.unit_pre_forward
+        if pre is not None:
+            pre("embed")
         x = F.embedding(tokens, self.tok_embeddings)
         residual = None
         hook = self.unit_grad_ready if torch.is_grad_enabled() else None
         for i, layer in enumerate(self.layers):
+            if pre is not None:
+                pre(f"layer{i}")
             if hook is not None and x.requires_grad:
                 # the gradient w.r.t. a block's input is the last thing its backward produces,
                 # so when it arrives every weight gradient of that block is complete
@@ -192,6 +201,8 @@ class Llama(nn.Module):
             x, residual = layer(x, residual, cs)
         if hook is not None and x.requires_grad:
             x.register_hook(lambda g: hook("head"))
+        if pre is not None:
+            pre("head")
         xn, _ = F.add_rmsnorm(x, residual, self.norm, self.cfg.norm_eps)
         logits = F.linear(xn, self.output)
         if targets is None:

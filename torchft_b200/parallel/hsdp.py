@@ -131,6 +131,12 @@ class HSDPEngine:
         self._futures: list = []
         if hasattr(model, "unit_grad_ready"):
             model.unit_grad_ready = self._unit_grad_ready
+        # parameter refresh (all-gather of updated slices) runs unit by unit on the communication
+        # stream; forward waits per unit, so only the first unit's exchange is exposed
+        self._gathered: Dict[str, "torch.cuda.Event"] = {}
+        self._prefetch = hasattr(model, "unit_pre_forward") and self.comm_stream is not None
+        if self._prefetch:
+            model.unit_pre_forward = self._unit_pre_forward
 
     # ------------------------------------------------------------------ slices
     def _shard_numel(self, u: Unit) -> int:
@@ -202,10 +208,38 @@ class HSDPEngine:
                 step=self.opt_step, grad_scale=grad_scale,
             )
 
-    def gather_parameters(self) -> None:
-        if self.comm.world > 1:
+    def gather_parameters(self, overlap: bool = False) -> None:
+        """All-gathers the owned parameter slices of every unit inside the replica group.
+
+        With ``overlap`` the exchange is queued on the communication stream and the model's
+        ``unit_pre_forward`` callback makes the compute stream wait unit by unit; otherwise the
+        calling stream sees all parameters complete when this returns.
+        """
+        if self.comm.world == 1:
+            return
+        if not (overlap and self._prefetch):
             for u in self.units:
                 self.comm.all_gather_(self.flat_param[u.offset : u.offset + u.numel], self._shard_numel(u))
+            return
+        current = torch.cuda.current_stream(self.device)
+        self.comm_stream.wait_stream(current)  # optimizer / recovery writes of the slices are ordered first
+        with torch.cuda.stream(self.comm_stream):
+            for u in self.units:
+                self.comm.all_gather_(self.flat_param[u.offset : u.offset + u.numel], self._shard_numel(u))
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                self._gathered[u.name] = ev
+
+    def _unit_pre_forward(self, name: str) -> None:
+        ev = self._gathered.pop(name, None)
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+
+    def _finish_gather(self) -> None:
+        """Units whose forward did not run (or ran without the callback) are waited for here."""
+        if self._gathered:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+            self._gathered.clear()
 
     # ------------------------------------------------------------------ whole step
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -216,9 +250,10 @@ class HSDPEngine:
         # group mate) just recovered: recovery rewrites only the owned slice of a rank, and which
         # ranks of a group recover differs per rank, so a collective inside load_state_dict would
         # not be symmetric.
-        self.gather_parameters()
+        self.gather_parameters(overlap=True)
         self.zero_grad()
         loss = self.model(tokens, targets)
+        self._finish_gather()
         loss.backward()
         self.sync_gradients()
         grad_scale = 1.0 / self.comm.world  # reduce-scatter sums over the shard group

@@ -63,6 +63,7 @@ def _lib_p2p() -> ctypes.CDLL:
             "tft_p2p_all_gather": head + [L, L, I, P],
             "tft_p2p_broadcast": head + [L, L, I, I, P],
             "tft_p2p_barrier": head + [P],
+            "tft_ag_gemm_bf16": head + [P, L, P, I, I, I, I, I, P, I, P],
         }.items():
             fn = getattr(lib, name)
             fn.argtypes = args
@@ -221,6 +222,7 @@ class NVLinkCommunicator:
         self._abort_dev = dev
         self._status_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stream = torch.cuda.Stream(device=self.device)
+        self._block_ready: Optional[torch.Tensor] = None  # per-block counters of the fused all-gather GEMM
 
     # ------------------------------------------------------------------ membership
     def configure(self, store: Store, rank: int, world: int, epoch_key: str) -> None:
@@ -333,6 +335,36 @@ class NVLinkCommunicator:
         code = _lib_p2p().tft_p2p_all_gather(*self._head(), self._offset(full), slice_bytes, self.max_blocks, _lib.stream_ptr())
         _lib.check(code, "tft_p2p_all_gather")
         _lib.count_launch()
+
+    def all_gather_linear(self, x: torch.Tensor, w_full: torch.Tensor, out: Optional[torch.Tensor] = None,
+                          copy_ctas: int = 16) -> torch.Tensor:
+        """``x @ w_full.T`` where ``w_full [N, K]`` lives in the symmetric heap and only this rank's
+        row slice of it is valid on entry: ONE kernel pulls the peers' slices over NVLink into
+        ``w_full`` and runs the tcgen05 GEMM on the blocks as they arrive (own rows first).
+
+        On return (stream order) ``w_full`` is completely gathered, so backward can use it as is.
+        Use a communicator (channel) of its own for this: it runs on the compute stream.
+        """
+        assert x.dtype == torch.bfloat16 and w_full.dtype == torch.bfloat16 and w_full.is_contiguous()
+        N, K = w_full.shape
+        x2 = x.reshape(-1, K)
+        assert x2.stride(1) == 1
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        if self.world == 1:
+            from torchft_b200.ops.gemm import gemm
+
+            gemm(x2, w_full, out)
+            return out.view(*x.shape[:-1], N)
+        if self._block_ready is None or self._block_ready.numel() < N // 256:
+            self._block_ready = torch.zeros(max(N // 256, 256), dtype=torch.int32, device=x.device)
+        code = _lib_p2p().tft_ag_gemm_bf16(
+            *self._head(), x2.data_ptr(), self._offset(w_full), out.data_ptr(), M, N, K, x2.stride(0), out.stride(0),
+            self._block_ready.data_ptr(), copy_ctas, _lib.stream_ptr())
+        _lib.check(code, "tft_ag_gemm_bf16")
+        _lib.count_launch()
+        return out.view(*x.shape[:-1], N)
 
     def broadcast_(self, t: torch.Tensor, root: int) -> None:
         if self.world == 1:
