@@ -134,16 +134,35 @@ reduce_scatter_kernel(Comm c, size_t off, long long slice_vec, float scale) {
   if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, 1);
   if (!wait_pad(c, START_PAD, c.seq, nullptr, flag)) return;
   const size_t base = off + static_cast<size_t>(c.rank) * slice_vec * 16;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < slice_vec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  // UNR * world peer loads are in flight per thread before the first add (see allreduce_kernel)
+  constexpr int UNR = 2;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < slice_vec;
+       i0 += stride * UNR) {
+    uint4 in[UNR][MAX_RANKS];
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k >= c.world) break;
-      const int p = (c.rank + k) % c.world;
-      Vec<T>::add(acc, ld_peer_v4(c.heap[p] + base + i * 16));
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        const int p = (c.rank + k) % c.world;
+        in[u][k] = make_uint4(0, 0, 0, 0);
+        if (i < slice_vec) in[u][k] = ld_peer_v4(c.heap[p] + base + i * 16);
+      }
     }
-    *reinterpret_cast<uint4*>(c.heap[c.rank] + base + i * 16) = Vec<T>::pack(acc, scale);
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= slice_vec) break;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        Vec<T>::add(acc, in[u][k]);
+      }
+      *reinterpret_cast<uint4*>(c.heap[c.rank] + base + i * 16) = Vec<T>::pack(acc, scale);
+    }
   }
   finish(c, flag);
 }
