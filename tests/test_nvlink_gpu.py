@@ -154,7 +154,7 @@ def test_process_group_nvlink():
 
 
 def _peer_absent(rank, world, port):
-    """Rank 1 configures but never launches the collective; rank 0's wait must run out cleanly."""
+    """Rank 1 stays away from the second collective; rank 0's device-side wait must run out cleanly."""
     import time
 
     from torch.distributed import ReduceOp, TCPStore
@@ -164,6 +164,10 @@ def _peer_absent(rank, world, port):
     store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
     pg = ProcessGroupNVLink(timeout=timedelta(seconds=1))
     pg.configure(f"127.0.0.1:{port}/absent/1", rank, world)
+    # the first collective of a membership meets on the host; do it together
+    first = torch.ones(1024, device="cuda")
+    pg.allreduce([first], ReduceOp.SUM).get_future().wait()
+    assert torch.all(first == float(world)).item()
     if rank == 0:
         t = torch.ones(1024, device="cuda")
         t0 = time.time()
@@ -339,3 +343,64 @@ def test_all_gather_fused_gemm_two_gpus():
 def test_all_gather_fused_gemm_four_gpus():
     _need_gpus(4)
     _spawn(_ag_gemm, 4)
+
+
+def _diloco_outer(rank, world, port):
+    """One-kernel DiLoCo outer step against the same arithmetic in fp32 PyTorch."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, SymmetricHeap
+
+    store = PrefixStore("dil", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False))
+    heap = SymmetricHeap.get(256 << 20)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=20))
+    comm.configure(store, rank, world, "epoch-diloco")
+    lr, mu = 0.7, 0.9
+    for dtype, n, tol in ((torch.bfloat16, 8 * 100003, 3e-2), (torch.float32, 4 * 50021, 1e-5)):
+        gen = lambda seed: torch.Generator(device="cuda").manual_seed(seed)  # noqa: E731
+        glob = torch.randn(n, device="cuda", generator=gen(3)).to(dtype)
+        locals_ = [(glob.float() + 0.05 * torch.randn(n, device="cuda", generator=gen(10 + r))).to(dtype) for r in range(world)]
+        local, grad = heap.alloc(n, dtype), heap.alloc(n, dtype)
+        g_in, g_out = glob.clone(), torch.zeros_like(glob)
+        m_in = torch.full((n,), 123.0, device="cuda")  # ignored on the first step
+        m_out = torch.zeros(n, device="cuda")
+        # step 1: everybody contributes, first use of the momentum
+        local.copy_(locals_[rank])
+        comm.diloco_outer_(local, grad, g_in, m_in, g_out, m_out, inv_n=1.0 / world, lr=lr, momentum=mu, nesterov=True, first=True)
+        torch.cuda.synchronize()
+        comm.check()
+        g_ref = sum(x.float() for x in locals_) / world - glob.float()
+        assert (grad.float() - g_ref).abs().max().item() < tol
+        g_used = grad.float()  # the kernel keeps using the rounded average
+        b_ref = g_used
+        w_ref = glob.float() - lr * (g_used + mu * b_ref)
+        assert (m_out - b_ref).abs().max().item() < 1e-6
+        assert (g_out.float() - w_ref).abs().max().item() < tol
+        assert torch.equal(g_in, glob), "inputs of a step must stay untouched until the commit"
+        # step 2: rank 0 takes part without contributing; buffers swapped as after a commit
+        locals2 = [(g_out.float() + 0.05 * torch.randn(n, device="cuda", generator=gen(20 + r))).to(dtype) for r in range(world)]
+        # every rank needs identical inputs: rebuild them from rank-independent seeds and the shared reference
+        w1 = w_ref.to(dtype)
+        g_in2, m_in2 = w1.clone(), b_ref.clone()
+        g_out2, m_out2 = torch.zeros_like(g_in2), torch.zeros_like(m_in2)
+        locals2 = [(w1.float() + 0.05 * torch.randn(n, device="cuda", generator=gen(20 + r))).to(dtype) for r in range(world)]
+        local.copy_(locals2[rank])
+        contributors = [r for r in range(world) if r != 0]
+        comm.diloco_outer_(local, grad, g_in2, m_in2, g_out2, m_out2, inv_n=1.0 / len(contributors), lr=lr, momentum=mu,
+                           nesterov=True, first=False, contribute=(rank != 0))
+        torch.cuda.synchronize()
+        comm.check()
+        g_ref2 = sum(locals2[r].float() for r in contributors) / len(contributors) - w1.float()
+        assert (grad.float() - g_ref2).abs().max().item() < tol
+        g_used2 = grad.float()
+        b2 = mu * m_in2 + g_used2
+        w2 = w1.float() - lr * (g_used2 + mu * b2)
+        assert (m_out2 - b2).abs().max().item() < 1e-5
+        assert (g_out2.float() - w2).abs().max().item() < tol
+        comm.barrier()
+    return "ok"
+
+
+def test_diloco_outer_step_single_kernel_two_gpus():
+    _need_gpus(2)
+    _spawn(_diloco_outer, 2)

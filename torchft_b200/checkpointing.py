@@ -25,7 +25,7 @@ from abc import ABC, abstractmethod
 from contextlib import contextmanager
 from datetime import timedelta
 from http.server import BaseHTTPRequestHandler
-from typing import Generator, Generic, List, Optional, TypeVar
+from typing import Dict, Generator, Generic, List, Optional, TypeVar
 
 import torch
 
@@ -46,10 +46,20 @@ def _compact(state: object) -> object:
     """
     from torch.utils._pytree import tree_map
 
+    side: Dict[torch.device, "torch.cuda.Stream"] = {}
+
     def one(x: object) -> object:
         if not isinstance(x, torch.Tensor):
             return x
         t = x.detach()
+        if t.device.type == "cuda":
+            # A stream of its own: the serving thread must not queue behind (or implicitly
+            # synchronise with) whatever the training thread has running on this device.
+            stream = side.get(t.device)
+            if stream is None:
+                stream = side[t.device] = torch.cuda.Stream(device=t.device)
+            with torch.cuda.device(t.device), torch.cuda.stream(stream):
+                return t.to("cpu")
         if t.device.type != "cpu":
             return t.to("cpu")
         if t.untyped_storage().nbytes() != t.numel() * t.element_size():

@@ -114,7 +114,7 @@ py::dict quorum_to_dict(const wire::Quorum& q) {
 PYBIND11_MODULE(TFT_MODULE_NAME, m) {
   m.doc() = "C++ control plane: lighthouse, manager server and clients";
 
-  py::class_<QuorumResult>(m, "QuorumResult")
+  py::class_<QuorumResult>(m, "QuorumResult", py::module_local())
       .def(py::init<>())
       .def_readwrite("quorum_id", &QuorumResult::quorum_id)
       .def_readwrite("replica_rank", &QuorumResult::replica_rank)
@@ -128,7 +128,7 @@ PYBIND11_MODULE(TFT_MODULE_NAME, m) {
       .def_readwrite("max_world_size", &QuorumResult::max_world_size)
       .def_readwrite("heal", &QuorumResult::heal);
 
-  py::class_<ManagerServer>(m, "Manager")
+  py::class_<ManagerServer>(m, "Manager", py::module_local())
       .def(py::init([](const std::string& replica_id, const std::string& lighthouse_addr, const std::string& hostname,
                        const std::string& bind, const std::string& store_addr, uint64_t world_size,
                        std::chrono::duration<double> heartbeat_interval, std::chrono::duration<double> connect_timeout) {
@@ -148,7 +148,7 @@ PYBIND11_MODULE(TFT_MODULE_NAME, m) {
         s.shutdown();
       });
 
-  py::class_<ManagerClient>(m, "ManagerClient")
+  py::class_<ManagerClient>(m, "ManagerClient", py::module_local())
       .def(py::init([](const std::string& addr, std::chrono::duration<double> connect_timeout) {
              try {
                py::gil_scoped_release release;
@@ -183,7 +183,7 @@ PYBIND11_MODULE(TFT_MODULE_NAME, m) {
            },
            py::arg("msg"), py::arg("timeout"));
 
-  py::class_<LighthouseClient>(m, "LighthouseClient")
+  py::class_<LighthouseClient>(m, "LighthouseClient", py::module_local())
       .def(py::init([](const std::string& addr, std::chrono::duration<double> connect_timeout) {
              try {
                py::gil_scoped_release release;
@@ -206,7 +206,7 @@ PYBIND11_MODULE(TFT_MODULE_NAME, m) {
            },
            py::arg("replica_id"), py::arg("timeout") = std::chrono::duration<double>(5.0));
 
-  py::class_<Lighthouse>(m, "Lighthouse")
+  py::class_<Lighthouse>(m, "Lighthouse", py::module_local())
       .def(py::init([](const std::string& bind, uint64_t min_replicas, std::optional<uint64_t> join_timeout_ms,
                        std::optional<uint64_t> quorum_tick_ms, std::optional<uint64_t> heartbeat_timeout_ms) {
              LighthouseOptions opt;

@@ -207,6 +207,166 @@ __global__ void barrier_kernel(Comm c) {
   finish(c, flag);
 }
 
+// ---------------------------------------------------------------- DiLoCo outer step, one kernel
+// Phase 1 (like the allreduce): rank r loads vectors of chunk r of the LOCAL weights from every
+// contributing replica, forms the averaged pseudo-gradient  mean_p(local_p) - global  in fp32 and
+// stores it (rounded to the weight type) into chunk r of every replica's gradient buffer.
+// Then all blocks of all replicas meet: the last block of a rank runs the end hand-shake with the
+// peers and releases the rank's other blocks through `phase_flag` (every block is resident: the
+// grid is at most one block per SM).
+// Phase 2 (local): Nesterov momentum and the new global weights for the WHOLE buffer,
+//     b = first ? g : mu * buf + g;   step = nesterov ? g + mu * b : b;   w = global - lr * step
+// written to `global_out` / `mom_out`, which the host swaps in only if the step commits.
+struct OuterArgs {
+  size_t off_local, off_g;
+  const void* global_in;
+  const float* mom_in;
+  void* global_out;
+  float* mom_out;
+  long long nvec;
+  float inv_n, lr, mu;
+  int nesterov, first, contribute;
+  uint32_t* phase_flag;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+diloco_outer_kernel(Comm c, OuterArgs a) {
+  __shared__ int flag[2];
+  __shared__ int is_last;
+  constexpr int N = Vec<T>::N;
+  if (blockIdx.x == 0) signal_pad(c, START_PAD, c.seq, a.contribute);
+  uint32_t mask = 0;
+  if (!wait_pad(c, START_PAD, c.seq, &mask, flag)) return;
+  const long long per = (a.nvec + c.world - 1) / c.world;
+  const long long lo = per * c.rank;
+  const long long hi = lo + per < a.nvec ? lo + per : a.nvec;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const uint4* gin = static_cast<const uint4*>(a.global_in);
+  constexpr int UNR = 2;
+  for (long long i0 = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < hi; i0 += stride * UNR) {
+    uint4 in[UNR][MAX_RANKS];
+    uint4 gl[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      gl[u] = make_uint4(0, 0, 0, 0);
+      if (i < hi) gl[u] = gin[i];
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        const int p = (c.rank + k) % c.world;
+        in[u][k] = make_uint4(0, 0, 0, 0);
+        if (i < hi && (mask & (1u << p))) in[u][k] = ld_peer_v4(c.heap[p] + a.off_local + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= hi) break;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        Vec<T>::add(acc, in[u][k]);
+      }
+      float gw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      Vec<T>::add(gw, gl[u]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] = acc[j] * a.inv_n - gw[j];
+      const uint4 out = Vec<T>::pack(acc, 1.f);
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        const int p = (c.rank + k) % c.world;
+        *reinterpret_cast<uint4*>(c.heap[p] + a.off_g + i * 16) = out;
+      }
+    }
+  }
+  // ---- every block of every replica has finished phase 1 before anyone reads its gradient buffer
+  const uint32_t go = flag_value(c.epoch, c.seq, 1), stop = flag_value(c.epoch, c.seq, 0);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t* counter = reinterpret_cast<uint32_t*>(c.heap[c.rank]) + c.pad_base + DONE_COUNTER;
+    const uint32_t ticket = atomicAdd(counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (is_last) {
+    signal_pad(c, END_PAD, c.seq, 0);
+    const bool ok = wait_pad(c, END_PAD, c.seq, nullptr, flag);
+    if (threadIdx.x == 0) st_release_gpu_u32(a.phase_flag, ok ? go : stop);
+    if (!ok) return;
+  } else {
+    if (threadIdx.x == 0) {
+      const unsigned long long t0 = now_ns();
+      uint32_t it = 0;
+      int ok = 0;
+      while (true) {
+        const uint32_t v = ld_acquire_gpu_u32(a.phase_flag);
+        if (v == go) { ok = 1; break; }
+        if (v == stop) break;
+        if ((++it & 63u) == 0) {
+          if (c.abort_word && *c.abort_word) {
+            if (c.status) atomicCAS(c.status, 0, static_cast<int>(kAborted));
+            break;
+          }
+          if (now_ns() - t0 > 2 * c.budget_ns) {  // the last block itself may wait a full budget for the peers
+            if (c.status) atomicCAS(c.status, 0, static_cast<int>(kTimeoutPeer));
+            break;
+          }
+          __nanosleep(100);
+        }
+      }
+      flag[0] = ok;
+    }
+    __syncthreads();
+    if (!flag[0]) return;
+  }
+  // ---- phase 2: local update of the whole buffer
+  const float4* min4 = reinterpret_cast<const float4*>(a.mom_in);
+  float4* mout4 = reinterpret_cast<float4*>(a.mom_out);
+  uint4* gout = static_cast<uint4*>(a.global_out);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < a.nvec; i += stride) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    Vec<T>::add(g, ld_peer_v4(c.heap[c.rank] + a.off_g + i * 16));
+    Vec<T>::add(w, gin[i]);
+    float b[8];
+    if (a.mu != 0.f) {
+#pragma unroll
+      for (int q = 0; q < N / 4; ++q) {
+        float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!a.first) m = min4[i * (N / 4) + q];
+        b[4 * q] = m.x; b[4 * q + 1] = m.y; b[4 * q + 2] = m.z; b[4 * q + 3] = m.w;
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        b[j] = a.first ? g[j] : a.mu * b[j] + g[j];
+        const float step = a.nesterov ? g[j] + a.mu * b[j] : b[j];
+        w[j] -= a.lr * step;
+      }
+#pragma unroll
+      for (int q = 0; q < N / 4; ++q)
+        mout4[i * (N / 4) + q] = make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; ++j) w[j] -= a.lr * g[j];
+    }
+    gout[i] = Vec<T>::pack(w, 1.f);
+  }
+}
+
 static int grid_for(long long nvec, int max_blocks) {
   long long b = (nvec + 511) / 512;
   if (b < 1) b = 1;
@@ -339,5 +499,43 @@ TFT_API int tft_p2p_pull(void* dst, const void* src, long long bytes, int max_bl
   const long long nvec = bytes / 16;
   tft::p2p::pull_copy_kernel<<<grid_for(nvec, max_blocks), 512, 0, stream>>>(
       static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nvec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// DiLoCo outer step fused with its allreduce (see diloco_outer_kernel).  `off_local` / `off_g` are heap
+// offsets of the local weights and of the gradient buffer (n elements each, 16-byte aligned, padded
+// to a multiple of 16 bytes); global_in/out and mom_in/out are ordinary device pointers of this rank.
+// phase_flag: one device uint32 owned by the caller (any value on entry).
+TFT_API int tft_diloco_outer(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                             const int* abort_word, int* status, long long off_local, long long off_g,
+                             const void* global_in, const float* mom_in, void* global_out, float* mom_out,
+                             long long n, int is_bf16, float inv_n, float lr, float mu, int nesterov, int first,
+                             int contribute, unsigned* phase_flag, int max_blocks, cudaStream_t stream) {
+  const long long bytes = n * (is_bf16 ? 2 : 4);
+  if ((off_local | off_g) & 15) return -1;
+  if ((reinterpret_cast<uintptr_t>(global_in) | reinterpret_cast<uintptr_t>(global_out) |
+       reinterpret_cast<uintptr_t>(mom_in) | reinterpret_cast<uintptr_t>(mom_out)) & 15)
+    return -1;
+  if (bytes % 16) return -2;  // the caller pads its flat buffers
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  OuterArgs a;
+  a.off_local = static_cast<size_t>(off_local);
+  a.off_g = static_cast<size_t>(off_g);
+  a.global_in = global_in; a.mom_in = mom_in; a.global_out = global_out; a.mom_out = mom_out;
+  a.nvec = bytes / 16;
+  a.inv_n = inv_n; a.lr = lr; a.mu = mu; a.nesterov = nesterov; a.first = first; a.contribute = contribute;
+  a.phase_flag = phase_flag;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  // all blocks wait for one another between the phases: never more blocks than SMs
+  int grid = grid_for(a.nvec, max_blocks < sm_count ? max_blocks : sm_count);
+  if (is_bf16)
+    diloco_outer_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(c, a);
+  else
+    diloco_outer_kernel<float><<<grid, 512, 0, stream>>>(c, a);
   return static_cast<int>(cudaGetLastError());
 }

@@ -231,6 +231,11 @@ class DiLoCo(LocalSGD):
             )
             if use_fused and self._fused is None:
                 raise RuntimeError("fused DiLoCo outer step requested but not available for this configuration")
+            if self._fused is not None:
+                pg = getattr(manager, "_pg", None)
+                if pg is not None and hasattr(pg, "fused_outer_step") and hasattr(pg, "heap"):
+                    # pseudo-gradient, allreduce and Nesterov update become one kernel
+                    self._fused.attach_nvlink(pg)
 
     def _perform_sync(self) -> None:
         if self._fused is not None:
@@ -260,6 +265,15 @@ class DiLoCo(LocalSGD):
     def _perform_sync_fused(self) -> None:
         fused = self._fused
         assert fused is not None
+        if fused.single_kernel:
+            fut = self._manager.run_collective(fused.launch_single_kernel, None)
+            fut.wait()
+            if self._manager.should_commit():
+                fused.commit_single_kernel()
+            else:
+                self._restore_parameters()
+            self._outer_optimizer.zero_grad()
+            return
         # kernel 1: comm = local - global (one pass), then averaged across replicas
         fused.compute_pseudogradients()
         self._average_grads()

@@ -221,6 +221,33 @@ class Manager:
             self.report_error(e)
             return _completed(tensor)
 
+    def run_collective(self, launch, result: T) -> "torch.futures.Future[T]":
+        """Runs a fused collective with the bookkeeping of ``allreduce``.
+
+        ``launch(pg, num_participants, contribute)`` starts the operation on the process group and
+        returns its work object.  Waits for the quorum first, does nothing once the step has
+        failed, and turns failures into ``report_error`` + ``result``.
+        """
+        if self.errored():
+            return _completed(result)
+        self.wait_quorum()
+        if self.errored():
+            return _completed(result)
+        try:
+            with trace_range("tft.collective"):
+                work = launch(self._pg, max(self.num_participants(), 1), self.is_participating())
+                fut = work.get_future()
+
+            def done(f: "torch.futures.Future[object]") -> T:
+                f.value()
+                return result
+
+            return self.wrap_future(fut.then(done), result)
+        except Exception as e:  # noqa: BLE001 - recorded, the step is discarded
+            self._logger.exception(f"got exception in collective -- skipping remaining: {e}")
+            self.report_error(e)
+            return _completed(result)
+
     def report_error(self, e: Exception) -> None:
         """Marks the current step as failed; it will not commit and the group reconfigures."""
         self._errored = e

@@ -1,4 +1,4 @@
-"""Fused DiLoCo outer step (``csrc/kernels/outer_step.cu``).
+"""Fused DiLoCo outer step (``csrc/kernels/elementwise.cu``, ``csrc/kernels/p2p_comm.cu``).
 
 Two kernels replace the reference's per-parameter ATen chain
 (``torchft/local_sgd.py:212-225``: sub, allreduce, divide, restore copy, SGD step, save
@@ -13,6 +13,13 @@ copy):
       param  = global;  backup = global
 
   reading g, global and buf once and writing param, backup and buf once.
+
+With the NVLink process group the whole outer step is ONE kernel (``diloco_outer_kernel``):
+every replica averages its chunk of the local weights straight out of the peers' memory,
+subtracts the global weights, hands the averaged pseudo-gradient chunk to everybody, and after
+an in-kernel barrier applies momentum and the update for the whole buffer into spare
+``global`` / momentum buffers that are swapped in after the commit vote
+(``FusedOuterStep.attach_nvlink``).
 
 The update runs only after the group voted to commit, so "no commit => weights
 untouched" is preserved.  The momentum buffers are the outer optimizer's own state
@@ -59,6 +66,79 @@ class FusedOuterStep:
                 buf = self._momentum[key][off : off + view.numel()].view(view.shape)
                 outer_optimizer.state[params[i]]["momentum_buffer"] = buf
         self._first = True
+        self._peer = None  # set by attach_nvlink
+
+    # ------------------------------------------------------------------ single-kernel path over NVLink
+    def attach_nvlink(self, pg) -> bool:
+        """Switches to the one-kernel outer step when all weights share one dtype and device."""
+        if len(self._comm.flat) != 1:
+            return False
+        key, flat = next(iter(self._comm.flat.items()))
+        n = flat.numel()
+        if (n * flat.element_size()) % 16:
+            return False
+        heap = pg.heap
+        base = flat.data_ptr()
+
+        def views_of(buf: torch.Tensor) -> List[torch.Tensor]:
+            out = []
+            for i in self._comm.groups[key]:
+                v = self._comm.views[i]
+                off = (v.data_ptr() - base) // flat.element_size()
+                out.append(buf[off : off + v.numel()].view(v.shape))
+            return out
+
+        local = heap.alloc(n, flat.dtype)
+        grad = heap.alloc(n, flat.dtype)
+        globals_ = [self._backup.flat[key], torch.empty_like(self._backup.flat[key])]
+        moms = [self._momentum[key], torch.zeros_like(self._momentum[key])]
+        self._peer = {
+            "key": key, "local": local, "grad": grad, "global": globals_, "mom": moms, "cur": 0,
+            "local_views": views_of(local),
+            "global_views": [views_of(g) for g in globals_],
+            "mom_views": [views_of(m) for m in moms],
+            "params": [self._params[i] for i in self._comm.groups[key]],
+            "idxs": list(self._comm.groups[key]),
+        }
+        return True
+
+    @property
+    def single_kernel(self) -> bool:
+        return self._peer is not None
+
+    def launch_single_kernel(self, pg, num_participants: int, contribute: bool):
+        """Packs the local weights and starts the fused kernel; returns the work object."""
+        st = self._peer
+        assert st is not None
+        with torch.no_grad():
+            torch._foreach_copy_(st["local_views"], [p.data for p in st["params"]])
+        g = self._opt.param_groups[0]
+        cur = st["cur"]
+        return pg.fused_outer_step(
+            [st["local"], st["grad"]],
+            local=st["local"], grad=st["grad"], global_in=st["global"][cur], mom_in=st["mom"][cur],
+            global_out=st["global"][1 - cur], mom_out=st["mom"][1 - cur], inv_n=1.0 / num_participants,
+            lr=float(g["lr"]), momentum=float(g.get("momentum", 0.0)), nesterov=bool(g.get("nesterov", False)),
+            first=self._first, contribute=contribute,
+        )
+
+    def commit_single_kernel(self) -> None:
+        """After a successful vote: the spare buffers become the global weights and momentum."""
+        st = self._peer
+        assert st is not None
+        cur = 1 - st["cur"]
+        st["cur"] = cur
+        key = st["key"]
+        self._backup.flat[key] = st["global"][cur]
+        self._momentum[key] = st["mom"][cur]
+        for j, i in enumerate(st["idxs"]):
+            self._backup.views[i] = st["global_views"][cur][j]
+            state = self._opt.state[self._params[i]]
+            if float(self._opt.param_groups[0].get("momentum", 0.0)) != 0.0:
+                state["momentum_buffer"] = st["mom_views"][cur][j]
+        with torch.no_grad():
+            torch._foreach_copy_([p.data for p in st["params"]], st["global_views"][cur])
+        self._first = False
 
     @classmethod
     def maybe_create(

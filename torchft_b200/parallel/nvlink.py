@@ -64,6 +64,7 @@ def _lib_p2p() -> ctypes.CDLL:
             "tft_p2p_broadcast": head + [L, L, I, I, P],
             "tft_p2p_barrier": head + [P],
             "tft_ag_gemm_bf16": head + [P, L, P, I, I, I, I, I, P, I, P],
+            "tft_diloco_outer": head + [L, L, P, P, P, P, L, I, F, F, F, I, I, I, P, I, P],
         }.items():
             fn = getattr(lib, name)
             fn.argtypes = args
@@ -223,6 +224,7 @@ class NVLinkCommunicator:
         self._status_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stream = torch.cuda.Stream(device=self.device)
         self._block_ready: Optional[torch.Tensor] = None  # per-block counters of the fused all-gather GEMM
+        self._phase_flag: Optional[torch.Tensor] = None  # phase word of the fused DiLoCo outer step
 
     # ------------------------------------------------------------------ membership
     def configure(self, store: Store, rank: int, world: int, epoch_key: str) -> None:
@@ -366,6 +368,32 @@ class NVLinkCommunicator:
         _lib.count_launch()
         return out.view(*x.shape[:-1], N)
 
+    def diloco_outer_(self, local: torch.Tensor, grad: torch.Tensor, global_in: torch.Tensor, mom_in: torch.Tensor,
+                      global_out: torch.Tensor, mom_out: torch.Tensor, *, inv_n: float, lr: float, momentum: float,
+                      nesterov: bool, first: bool, contribute: bool = True) -> None:
+        """DiLoCo outer step in one kernel: averaged pseudo-gradient over the replicas into ``grad``
+        (every rank), then momentum and new global weights into ``mom_out`` / ``global_out``.
+
+        ``local`` and ``grad`` are flat heap tensors of the weight dtype; the others are flat tensors
+        of this rank (``mom_*`` fp32).  Nothing that survives a failed step is modified: the caller
+        swaps the ``*_out`` buffers in after the commit vote.
+        """
+        assert local.dtype == grad.dtype == global_in.dtype == global_out.dtype
+        assert local.dtype in (torch.bfloat16, torch.float32)
+        assert mom_in.dtype == mom_out.dtype == torch.float32
+        n = local.numel()
+        assert grad.numel() == n and global_in.numel() == n and global_out.numel() == n
+        assert mom_in.numel() == n and mom_out.numel() == n
+        if self._phase_flag is None:
+            self._phase_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        code = _lib_p2p().tft_diloco_outer(
+            *self._head(), self._offset(local), self._offset(grad), global_in.data_ptr(), mom_in.data_ptr(),
+            global_out.data_ptr(), mom_out.data_ptr(), n, 1 if local.dtype == torch.bfloat16 else 0, inv_n, lr, momentum,
+            1 if nesterov else 0, 1 if first else 0, 1 if contribute else 0, self._phase_flag.data_ptr(), 132,
+            _lib.stream_ptr())
+        _lib.check(code, "tft_diloco_outer")
+        _lib.count_launch()
+
     def broadcast_(self, t: torch.Tensor, root: int) -> None:
         if self.world == 1:
             return
@@ -400,6 +428,8 @@ class ProcessGroupNVLink(ProcessGroup):
         self._staging = self._heap.alloc(staging_bytes, torch.uint8)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._configured = False
+        self._store: Optional[Store] = None
+        self._first_pending = False
 
     @property
     def communicator(self) -> NVLinkCommunicator:
@@ -409,6 +439,27 @@ class ProcessGroupNVLink(ProcessGroup):
         store = create_store_client(store_addr)
         self._comm.configure(store, rank, world_size, epoch_key=store_addr)
         self._configured = True
+        self._store = store
+        self._first_pending = world_size > 1
+
+    def _rendezvous(self) -> None:
+        """Host-side meeting before the FIRST collective of a membership.
+
+        Right after a reconfiguration the members are far apart in time: one may spend many
+        seconds fetching a checkpoint while the others are ready.  Meeting on the host first
+        keeps the ready ones from occupying their GPU with a kernel that only waits (and from
+        holding up copies that the checkpoint transfer needs on that GPU).  Later collectives
+        run in the lockstep of training and go straight to the device.
+        """
+        if not self._first_pending:
+            return
+        comm = self._comm
+        self._store.set(f"go/{comm.rank}", b"1")
+        try:
+            self._store.wait([f"go/{r}" for r in range(comm.world)], timedelta(milliseconds=comm.timeout_ms))
+        except Exception as e:  # noqa: BLE001 - c10d raises its own error type on expiry
+            raise TimeoutError(f"peers did not reach their first collective within {comm.timeout_ms} ms: {e}") from e
+        self._first_pending = False
 
     def abort(self) -> None:
         self._comm.abort()
@@ -424,6 +475,7 @@ class ProcessGroupNVLink(ProcessGroup):
         """Runs ``fn(buffer)`` per tensor on the communicator stream (staging when needed)."""
         if not self._configured:
             raise RuntimeError("torchft-nvlink process group used before configure()")
+        self._rendezvous()
         comm = self._comm
         current = torch.cuda.current_stream(comm.device)
         comm.stream.wait_stream(current)
@@ -464,6 +516,26 @@ class ProcessGroupNVLink(ProcessGroup):
         """Sum, scaling and the zero contribution of a non-participating rank in one kernel."""
         return self._launch([tensor], lambda b: self._comm.allreduce_(b, scale, contribute), "allreduce")
 
+    def fused_outer_step(self, keep: List[torch.Tensor], **kwargs) -> Work:
+        """``NVLinkCommunicator.diloco_outer_`` on the communicator stream, as a work object."""
+        if not self._configured:
+            raise RuntimeError("torchft-nvlink process group used before configure()")
+        self._rendezvous()
+        comm = self._comm
+        comm.stream.wait_stream(torch.cuda.current_stream(comm.device))
+        with torch.cuda.stream(comm.stream):
+            comm.diloco_outer_(**kwargs)
+            self._status_host.copy_(comm._status_dev, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(comm.stream)
+        fut: Future = Future()
+        _WATCHER.submit(event, fut, keep, self._status_host, "diloco_outer")
+        return _StreamWork(event, fut)
+
+    @property
+    def heap(self) -> SymmetricHeap:
+        return self._heap
+
     def broadcast(self, tensor_list: List[torch.Tensor], opts: object) -> Work:
         root = int(getattr(opts, "rootRank", 0))
         return self._launch(tensor_list, lambda b: self._comm.broadcast_(b, root), "broadcast")
@@ -472,6 +544,7 @@ class ProcessGroupNVLink(ProcessGroup):
         comm = self._comm
         if not self._configured:
             raise RuntimeError("torchft-nvlink process group used before configure()")
+        self._rendezvous()
         current = torch.cuda.current_stream(comm.device)
         comm.stream.wait_stream(current)
         with torch.cuda.stream(comm.stream):
