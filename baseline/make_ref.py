@@ -38,7 +38,7 @@ def main() -> None:
         shutil.copy2(src, DEST / src.name)
     shutil.copy2(REF_SRC / "torchft.pyi", DEST / "torchft.pyi")
     control = ROOT / "torchft_b200" / "csrc" / "control"
-    sources = [str(p) for p in sorted(control.glob("*.cc")) if p.name != "lighthouse_main.cc"]
+    sources = [str(p) for p in sorted(control.glob("*.cc")) if p.name not in ("lighthouse_main.cc", "stress_main.cc")]
     out = DEST / ("torchft" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
     cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"
     cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-pthread", "-shared", "-fvisibility=hidden", "-Wl,-Bsymbolic",

@@ -143,6 +143,42 @@ def run_arm(arm: str, args, rank: int, world: int, heap) -> dict:
             "param_checksum": round(checksum, 2)}
 
 
+def kernel_arm(rank: int, world: int, heap) -> dict:
+    """Device time of the one-kernel outer step alone (CUDA events, max over ranks)."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator
+
+    store = PrefixStore("dk", TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), is_master=False,
+                                       wait_for_workers=False))
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=30))
+    comm.configure(store, rank, world, "diloco-kernel")
+    n = 1498482688  # parameters of the Llama 1B shape
+    local, grad = heap.alloc(n, torch.bfloat16), heap.alloc(n, torch.bfloat16)
+    g = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    m = [torch.zeros(n, device="cuda") for _ in range(2)]
+    local.normal_(0, 0.02)
+    times = []
+    for it in range(6):
+        dist.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        comm.diloco_outer_(local, grad, g[it & 1], m[it & 1], g[1 - (it & 1)], m[1 - (it & 1)], inv_n=1.0 / world, lr=0.7,
+                           momentum=0.9, nesterov=True, first=(it == 0))
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    comm.check()
+    t = torch.tensor([statistics.median(times[2:])], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    link_bytes = 2.0 * n * (world - 1) / world          # per direction: chunk loads in, averaged chunk stores out
+    hbm_bytes = n * (2 + 2 + 4 + 2 + 4) + 4.0 * n / world + 2.0 * n  # phase 2; phase 1 own chunk + global; gradient stores landing here
+    roof_ms = (link_bytes / 770e9 + hbm_bytes / 6548.5e9) * 1e3  # the phases run one after the other
+    return {"arm": "kernel", "replicas": world, "params": n, "kernel_ms": round(ms, 3), "roofline_ms": round(roof_ms, 3),
+            "of_roofline": round(roof_ms / ms, 3)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama_1b", choices=["llama_1b", "tiny"])
@@ -159,7 +195,7 @@ def main() -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    dist.init_process_group("gloo", timeout=timedelta(seconds=300))
+    dist.init_process_group("cpu:gloo,cuda:nccl" if "kernel" in args.arms else "gloo", timeout=timedelta(seconds=300))
     from torchft_b200.parallel.nvlink import SymmetricHeap
 
     heap = SymmetricHeap.get(12 << 30)
@@ -168,7 +204,7 @@ def main() -> None:
             if rank == 0:
                 print(json.dumps({"arm": "reference", "unavailable": "baseline/_ref missing"}), flush=True)
             continue
-        res = run_arm(arm, args, rank, world, heap)
+        res = kernel_arm(rank, world, heap) if arm == "kernel" else run_arm(arm, args, rank, world, heap)
         if rank == 0:
             print(json.dumps(res), flush=True)
         dist.barrier()

@@ -1,0 +1,141 @@
+// Stress harness for the control plane, meant to be built with -fsanitize=thread or
+// -fsanitize=address (tests/test_sanitizers.py does both).  One process hosts a lighthouse,
+// several replica-group manager servers and one client thread per (group, local rank); the
+// threads run quorum + should_commit rounds against each other while another thread polls the
+// dashboard.  Half way through one group goes away (its threads stop, its server shuts down),
+// so the survivors exercise the heartbeat-expiry and shrinking-quorum paths.  Exit code 0
+// means every answer was consistent; the sanitizer reports races and memory errors itself.
+//
+// The reference relies on Rust's ownership rules for this (src/lighthouse.rs, src/manager.rs);
+// a C++ control plane needs a dynamic check instead.
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <memory>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "lighthouse.h"
+#include "manager.h"
+
+using namespace tft;
+using net::Millis;
+
+namespace {
+
+std::atomic<int> g_failures{0};
+
+void fail(const std::string& what) {
+  std::fprintf(stderr, "stress: %s\n", what.c_str());
+  g_failures.fetch_add(1);
+}
+
+std::string http_get(int port, const std::string& path) {
+  std::string err;
+  net::HostPort hp{"127.0.0.1", port};
+  const int fd = net::connect_to(hp, Millis(2000), &err);
+  if (fd < 0) return "";
+  const std::string req = "GET " + path + " HTTP/1.1\r\nHost: x\r\nConnection: close\r\n\r\n";
+  std::string out;
+  size_t sent = 0;
+  while (sent < req.size()) {
+    const ssize_t n = ::send(fd, req.data() + sent, req.size() - sent, MSG_NOSIGNAL);
+    if (n <= 0) break;
+    sent += static_cast<size_t>(n);
+  }
+  char buf[4096];
+  while (sent == req.size()) {
+    const ssize_t n = ::recv(fd, buf, sizeof(buf), 0);
+    if (n <= 0) break;
+    out.append(buf, static_cast<size_t>(n));
+  }
+  ::close(fd);
+  return out;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  const int groups = argc > 1 ? std::atoi(argv[1]) : 3;
+  const int ranks = argc > 2 ? std::atoi(argv[2]) : 2;
+  const int rounds = argc > 3 ? std::atoi(argv[3]) : 24;
+  net::set_log_enabled(false);
+
+  LighthouseOptions opt;
+  opt.bind = "[::]:0";
+  opt.min_replicas = 1;
+  opt.join_timeout_ms = 200;
+  opt.quorum_tick_ms = 5;
+  opt.heartbeat_timeout_ms = 300;
+  auto lighthouse = std::make_unique<Lighthouse>(opt);
+  const std::string lh_addr = "http://127.0.0.1:" + std::to_string(lighthouse->port());
+
+  std::vector<std::unique_ptr<ManagerServer>> managers;
+  for (int g = 0; g < groups; ++g)
+    managers.push_back(std::make_unique<ManagerServer>("group" + std::to_string(g), lh_addr, "127.0.0.1", "[::]:0",
+                                                       "store" + std::to_string(g), static_cast<uint64_t>(ranks),
+                                                       Millis(20), Millis(5000)));
+
+  std::atomic<bool> stop_dashboard{false};
+  std::thread dashboard([&] {
+    while (!stop_dashboard.load()) {
+      const std::string page = http_get(lighthouse->port(), "/status");
+      if (!page.empty() && page.find("200") == std::string::npos) fail("dashboard did not answer 200");
+      std::this_thread::sleep_for(Millis(3));
+    }
+  });
+
+  const int leaving_group = groups - 1;
+  const int leave_after = rounds / 2;
+  std::vector<std::thread> workers;
+  for (int g = 0; g < groups; ++g) {
+    for (int r = 0; r < ranks; ++r) {
+      workers.emplace_back([&, g, r] {
+        try {
+          ManagerClient client(managers[g]->address(), Millis(5000));
+          int64_t step = 0;
+          const int my_rounds = (g == leaving_group && groups > 1) ? leave_after : rounds;
+          for (int round = 0; round < my_rounds; ++round) {
+            const auto q = client.quorum(r, step, "meta" + std::to_string(r), false, Millis(20000));
+            if (q.replica_world_size < 1 || q.replica_world_size > groups) fail("impossible replica_world_size");
+            if (q.replica_rank < 0 || q.replica_rank >= q.replica_world_size) fail("replica_rank out of range");
+            if (q.max_step < step) fail("max_step went backwards");
+            if (client.checkpoint_metadata(r, Millis(5000)) != "meta" + std::to_string(r)) fail("metadata mix-up");
+            // one rank of one group votes no every fifth round: the whole group must see false
+            const bool group_vote_no = (round % 5 == 4);
+            const bool my_vote = !(group_vote_no && r == 0);
+            const bool decision = client.should_commit(r, step, my_vote, Millis(20000));
+            if (decision != !group_vote_no) fail("should_commit decision differs from the AND of the votes");
+            if (decision) ++step;
+          }
+        } catch (const std::exception& e) {
+          fail(std::string("worker exception: ") + e.what());
+        }
+      });
+    }
+  }
+  // the leaving group's workers finish first; take its server down while the others keep going
+  if (groups > 1) {
+    for (int r = 0; r < ranks; ++r) workers[leaving_group * ranks + r].join();
+    managers[leaving_group]->shutdown();
+    managers[leaving_group].reset();
+  }
+  for (int g = 0; g < groups; ++g) {
+    if (g == leaving_group && groups > 1) continue;
+    for (int r = 0; r < ranks; ++r) workers[g * ranks + r].join();
+  }
+  stop_dashboard.store(true);
+  dashboard.join();
+  for (auto& m : managers)
+    if (m) m->shutdown();
+  managers.clear();
+  lighthouse->shutdown();
+  lighthouse.reset();
+  const int failures = g_failures.load();
+  std::fprintf(stderr, "stress: %d failure(s)\n", failures);
+  return failures == 0 ? 0 : 1;
+}

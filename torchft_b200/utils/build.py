@@ -104,7 +104,7 @@ def build_control(force: bool = False) -> Path:
     import pybind11
 
     LIB_DIR.mkdir(parents=True, exist_ok=True)
-    sources = sorted(p for p in CONTROL_SRC.glob("*.cc") if p.name not in ("lighthouse_main.cc",))
+    sources = sorted(p for p in CONTROL_SRC.glob("*.cc") if p.name not in ("lighthouse_main.cc", "stress_main.cc"))
     headers = sorted(CONTROL_SRC.glob("*.h"))
     out = control_module_path()
     newest = max(_newest(sources), _newest(headers))
