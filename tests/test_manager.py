@@ -316,3 +316,35 @@ def test_send_checkpoint_to_recovering_peers(env):
     assert kwargs["state_dict"]["user"] == {"user": "state"}
     manager.should_commit()
     assert transport.disallow_checkpoint.call_count == 1
+
+
+def test_run_collective_bookkeeping(env):
+    """A fused collective gets the allreduce treatment: quorum first, participants passed, errors recorded."""
+    manager, pg, _ = env()
+    manager._client.quorum.return_value = quorum_result()
+    manager._client.should_commit.return_value = True
+    manager.start_quorum()
+    seen = {}
+
+    def launch(group, n, contribute):
+        seen.update(pg=group, n=n, contribute=contribute)
+        return _DummyWork([torch.zeros(1)])
+
+    assert manager.run_collective(launch, "result").wait() == "result"
+    assert seen == {"pg": pg, "n": 2, "contribute": True}
+    assert manager.errored() is None and manager.should_commit()
+
+    # a launch that raises: recorded, the default comes back, the step does not commit
+    manager.start_quorum()
+
+    def broken(group, n, contribute):
+        raise RuntimeError("launch failed")
+
+    assert manager.run_collective(broken, "fallback").wait() == "fallback"
+    assert isinstance(manager.errored(), RuntimeError)
+    # once the step has failed further collectives are skipped
+    seen.clear()
+    manager.run_collective(launch, None).wait()
+    assert seen == {}
+    manager._client.should_commit.return_value = False
+    assert not manager.should_commit()
