@@ -11,10 +11,15 @@ Lighthouse, QuorumResult).  This script
    interface of ``torchft/torchft.pyi``.
 
 Everything the benchmark measures (NCCL allreduce + divide, DDP bucketing, the Manager state
-machine, HTTP checkpoint transport) then runs from the reference's Python.  Run it where
-``/root/reference`` is mounted:  ``python baseline/make_ref.py``
+machine, HTTP checkpoint transport) then runs from the reference's Python.
+
+    python baseline/make_ref.py [path/to/reference/checkout]
+
+Without an argument the checkout is looked for in ``$TORCHFT_REFERENCE_DIR`` and then in a
+directory called ``reference`` next to this repository.
 """
 
+import os
 import shutil
 import subprocess
 import sys
@@ -22,7 +27,16 @@ import sysconfig
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
-REF_SRC = Path("/root/reference/torchft")
+
+def _reference_checkout() -> Path:
+    if len(sys.argv) > 1:
+        return Path(sys.argv[1])
+    if os.environ.get("TORCHFT_REFERENCE_DIR"):
+        return Path(os.environ["TORCHFT_REFERENCE_DIR"])
+    return ROOT.parent / "reference"
+
+
+REF_SRC = _reference_checkout() / "torchft"
 DEST = ROOT / "baseline" / "_ref" / "torchft"
 
 
