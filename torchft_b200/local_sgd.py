@@ -29,7 +29,7 @@ from __future__ import annotations
 
 import logging
 from types import TracebackType
-from typing import Dict, List, Optional, Tuple, Type
+from typing import Callable, Dict, List, Optional, Tuple, Type
 
 import torch
 from torch import nn, optim
@@ -43,7 +43,10 @@ logger: logging.Logger = logging.getLogger(__name__)
 class _FlatBuckets:
     """Flat per-(dtype, device) buffers mirroring a list of parameters."""
 
-    def __init__(self, params: List[torch.Tensor], device: Optional[torch.device], pin_memory: bool) -> None:
+    def __init__(self, params: List[torch.Tensor], device: Optional[torch.device], pin_memory: bool,
+                 alloc: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None) -> None:
+        """``alloc(numel, dtype)``, when given, provides the CUDA buffers (e.g. from a symmetric heap so
+        that peer-memory collectives reduce them in place); it may raise to fall back to ``torch.zeros``."""
         self.params = params
         self.groups: Dict[Tuple[torch.dtype, torch.device], List[int]] = {}
         for i, p in enumerate(params):
@@ -62,7 +65,14 @@ class _FlatBuckets:
                 cursor += (params[i].numel() + align - 1) // align * align
             total = cursor
             dev = device if device is not None else pdev
-            buf = torch.zeros(total, dtype=dtype, device=dev)
+            buf = None
+            if alloc is not None and dev.type == "cuda":
+                try:
+                    buf = alloc(total, dtype)
+                except RuntimeError as e:  # heap too small: ordinary memory works too, through staging
+                    logger.info(f"flat bucket of {total} elements does not fit the peer heap ({e}); using device memory")
+            if buf is None:
+                buf = torch.zeros(total, dtype=dtype, device=dev)
             if pin_memory and dev.type == "cpu" and torch.cuda.is_available():
                 buf = buf.pin_memory()
             self.flat[key] = buf
@@ -124,7 +134,9 @@ class LocalSGD:
             n: v for n, v in zip(self._names, self._backup.views)  # type: ignore[misc]
         }
         # communication buckets on the parameters' own devices
-        self._comm = _FlatBuckets(self._params, None, False)
+        # communication buckets live in the process group's peer-addressable heap when it has one
+        heap = getattr(getattr(manager, "_pg", None), "heap", None)
+        self._comm = _FlatBuckets(self._params, None, False, alloc=heap.alloc if heap is not None else None)
         self._hooks: List[RemovableHandle] = []
         self._save_parameters()
 

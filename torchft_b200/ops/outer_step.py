@@ -88,8 +88,12 @@ class FusedOuterStep:
                 out.append(buf[off : off + v.numel()].view(v.shape))
             return out
 
-        local = heap.alloc(n, flat.dtype)
-        grad = heap.alloc(n, flat.dtype)
+        try:
+            local = heap.alloc(n, flat.dtype)
+            # the communication bucket doubles as the gradient buffer when it already lives in the heap
+            grad = flat if heap.offset_of(flat) is not None else heap.alloc(n, flat.dtype)
+        except RuntimeError:
+            return False  # heap too small: stay on the two-kernel path
         globals_ = [self._backup.flat[key], torch.empty_like(self._backup.flat[key])]
         moms = [self._momentum[key], torch.zeros_like(self._momentum[key])]
         self._peer = {
