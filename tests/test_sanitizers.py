@@ -14,7 +14,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = os.path.join(ROOT, "torchft_b200", "csrc", "control")
-SOURCES = ["wire.cc", "net.cc", "quorum.cc", "lighthouse.cc", "manager.cc", "cli.cc", "stress_main.cc"]
+SOURCES = ["wire.cc", "net.cc", "h2.cc", "quorum.cc", "lighthouse.cc", "manager.cc", "cli.cc", "stress_main.cc"]
 
 
 def _compiler():
@@ -37,8 +37,9 @@ def test_control_plane_under_sanitizer(tmp_path, sanitizer, marker):
         pytest.skip(f"-fsanitize={sanitizer} runtime not installed")
     assert build.returncode == 0, build.stderr[-3000:]
     env = dict(os.environ, TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1", ASAN_OPTIONS="detect_leaks=1")
-    run = subprocess.run([str(exe), "4", "3", "40"], capture_output=True, text=True, timeout=300, env=env)
-    assert marker not in run.stderr, run.stderr[-6000:]
-    assert "LeakSanitizer" not in run.stderr, run.stderr[-6000:]
-    assert run.returncode == 0, run.stderr[-3000:]
-    assert "stress: 0 failure(s)" in run.stderr
+    for protocol in ("framed", "grpc"):  # the length-prefixed transport and gRPC over HTTP/2
+        run = subprocess.run([str(exe), "4", "3", "40", protocol], capture_output=True, text=True, timeout=300, env=env)
+        assert marker not in run.stderr, protocol + "\n" + run.stderr[-6000:]
+        assert "LeakSanitizer" not in run.stderr, protocol + "\n" + run.stderr[-6000:]
+        assert run.returncode == 0, protocol + "\n" + run.stderr[-3000:]
+        assert "stress: 0 failure(s)" in run.stderr

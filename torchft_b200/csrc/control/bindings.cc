@@ -10,6 +10,7 @@
 #include <csignal>
 
 #include "cli.h"
+#include "h2.h"
 #include "lighthouse.h"
 #include "manager.h"
 #include "quorum.h"
@@ -335,6 +336,40 @@ PYBIND11_MODULE(TFT_MODULE_NAME, m) {
         py::arg("max_retries") = py::none());
 
   m.def("set_log_enabled", &net::set_log_enabled);
+
+  // Wire protocol of the clients created afterwards: "framed" (default) or "grpc" (HTTP/2, the
+  // reference's format).  Servers accept both on the same port at all times.
+  m.def("set_rpc_protocol", [](const std::string& name) {
+    try {
+      net::set_rpc_protocol(name);
+    } catch (const std::invalid_argument& e) {
+      throw py::value_error(e.what());
+    }
+  });
+  m.def("rpc_protocol", &net::rpc_protocol);
+
+  // HPACK pieces, exposed for tests against RFC 7541 vectors and other HTTP/2 stacks.
+  m.def("huffman_encode", [](const py::bytes& b) { return py::bytes(net::h2::huffman_encode(std::string(b))); });
+  m.def("huffman_decode", [](const py::bytes& b) -> py::object {
+    const std::string in(b);
+    std::string out;
+    if (!net::h2::huffman_decode(reinterpret_cast<const uint8_t*>(in.data()), in.size(), &out)) return py::none();
+    return py::bytes(out);
+  });
+  m.def("hpack_encode", [](const std::vector<std::pair<std::string, std::string>>& headers, bool huffman) {
+    std::vector<net::h2::Header> hs;
+    for (const auto& kv : headers) hs.push_back({kv.first, kv.second});
+    return py::bytes(net::h2::hpack_encode(hs, huffman));
+  }, py::arg("headers"), py::arg("huffman") = true);
+  py::class_<net::h2::HpackDecoder>(m, "HpackDecoder", py::module_local())
+      .def(py::init<>())
+      .def("decode", [](net::h2::HpackDecoder& self, const py::bytes& block) -> py::object {
+        std::vector<net::h2::Header> out;
+        if (!self.decode(std::string(block), &out)) return py::none();
+        py::list result;
+        for (const auto& h : out) result.append(py::make_tuple(py::bytes(h.name), py::bytes(h.value)));
+        return result;
+      });
 
   // Wire codec round trips for interop tests against other protobuf implementations.
   m.def("encode_manager_quorum_response", [](const QuorumResult& r) {

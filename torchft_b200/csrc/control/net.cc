@@ -1,5 +1,7 @@
 #include "net.h"
 
+#include "h2.h"
+
 #include <arpa/inet.h>
 #include <errno.h>
 #include <fcntl.h>
@@ -41,14 +43,14 @@ uint16_t get_u16(const char* p) {
   return uint16_t((u[0] << 8) | u[1]);
 }
 
-enum IoResult { kIoOk, kIoTimeout, kIoClosed };
-
 int remaining_ms(Clock::time_point deadline) {
   if (deadline == Clock::time_point::max()) return 200;
   auto left = std::chrono::duration_cast<Millis>(deadline - Clock::now()).count();
   if (left <= 0) return 0;
   return static_cast<int>(std::min<long long>(left, 200));
 }
+
+}  // namespace
 
 IoResult read_exact(int fd, char* buf, size_t n, Clock::time_point deadline,
                     const std::atomic<bool>* stopping) {
@@ -95,6 +97,10 @@ IoResult write_all(int fd, const char* buf, size_t n, Clock::time_point deadline
   return kIoOk;
 }
 
+namespace {
+
+std::atomic<int> g_rpc_protocol{-1};  // -1: not decided yet (environment), 0 framed, 1 grpc
+
 void set_nodelay(int fd) {
   int one = 1;
   ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
@@ -104,6 +110,22 @@ void set_nodelay(int fd) {
 }  // namespace
 
 void set_log_enabled(bool enabled) { g_log_enabled.store(enabled); }
+
+void set_rpc_protocol(const std::string& name) {
+  if (name == "framed") g_rpc_protocol.store(0);
+  else if (name == "grpc") g_rpc_protocol.store(1);
+  else throw std::invalid_argument("unknown RPC protocol '" + name + "' (framed or grpc)");
+}
+
+std::string rpc_protocol() {
+  int v = g_rpc_protocol.load();
+  if (v < 0) {
+    const char* env = std::getenv("TORCHFT_B200_RPC");
+    v = (env != nullptr && std::string(env) == "grpc") ? 1 : 0;
+    g_rpc_protocol.store(v);
+  }
+  return v == 1 ? "grpc" : "framed";
+}
 
 void log_info(const std::string& module, const std::string& msg) {
   if (!g_log_enabled.load()) return;
@@ -351,6 +373,7 @@ int connect_to(const HostPort& hp, Millis timeout, std::string* err) {
 
 bool CallContext::cancelled() const {
   if (stopping && stopping->load()) return true;
+  if (stream_cancelled && stream_cancelled->load()) return true;
   if (deadline != Clock::time_point::max() && Clock::now() >= deadline) return true;
   if (fd >= 0) {
     char c;
@@ -417,6 +440,15 @@ void Server::serve(int fd) {
   if (read_exact(fd, magic, 4, Clock::time_point::max(), &stopping_) != kIoOk) return;
   if (std::memcmp(magic, "TFT1", 4) == 0) {
     serve_rpc(fd);
+  } else if (std::memcmp(magic, "PRI ", 4) == 0) {
+    // HTTP/2 client preface: gRPC
+    h2::serve_connection(fd, std::string(magic, 4), stopping_,
+                         [this](const std::string& path, const CallContext& ctx, const std::string& payload,
+                                std::string* resp) -> Status {
+                           auto it = methods_.find(path);
+                           if (it == methods_.end()) return Status::Error(12 /*Unimplemented*/, "unknown method " + path);
+                           return it->second(ctx, payload, resp);
+                         });
   } else {
     serve_http(fd, std::string(magic, 4));
   }
@@ -543,6 +575,7 @@ void Server::serve_http(int fd, const std::string& first) {
 // ---------------------------------------------------------------- Client
 Client::Client(const std::string& addr, Millis connect_timeout)
     : addr_(addr), hp_(parse_address(addr)), connect_timeout_(connect_timeout) {
+  grpc_ = rpc_protocol() == "grpc";
   std::lock_guard<std::mutex> g(mu_);
   ensure_connected();
 }
@@ -550,6 +583,11 @@ Client::Client(const std::string& addr, Millis connect_timeout)
 Client::~Client() { close_fd(); }
 
 void Client::close_fd() {
+  if (h2_) {  // the HTTP/2 connection owns the socket
+    h2_.reset();
+    fd_ = -1;
+    return;
+  }
   if (fd_ >= 0) {
     ::close(fd_);
     fd_ = -1;
@@ -569,12 +607,24 @@ void Client::ensure_connected() {
     return fd_ >= 0;
   });
   if (!ok) throw RpcError(kUnavailable, "failed to connect to " + addr_ + ": " + err);
+  if (grpc_) h2_ = std::make_shared<h2::ClientConnection>(fd_, hp_.host + ":" + std::to_string(hp_.port));
+}
+
+std::string Client::call_grpc(const std::string& path, const std::string& payload, std::optional<Millis> timeout) {
+  auto* conn = static_cast<h2::ClientConnection*>(h2_.get());
+  std::string resp;
+  bool broken = false;
+  const Status st = conn->call(path, payload, timeout, &resp, &broken);
+  if (broken) close_fd();
+  if (!st.ok()) throw RpcError(st.code, st.message);
+  return resp;
 }
 
 std::string Client::call(const std::string& path, const std::string& payload,
                          std::optional<Millis> timeout) {
   std::lock_guard<std::mutex> g(mu_);
   ensure_connected();
+  if (grpc_) return call_grpc(path, payload, timeout);
   const auto deadline = timeout ? Clock::now() + *timeout : Clock::time_point::max();
   std::string body;
   put_u16(&body, static_cast<uint16_t>(path.size()));

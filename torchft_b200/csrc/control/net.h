@@ -6,6 +6,9 @@
 //     u32 len | u8 status code | u16 msg_len | msg | protobuf payload.  Method paths
 //     ("/torchft.ManagerService/Quorum") and status codes are those of gRPC.
 //   * HTTP/1.1 for the dashboard.
+//   * gRPC over HTTP/2 (connections that open with the HTTP/2 client preface), see h2.h: the
+//     reference's own wire format.  Servers always accept it; clients use it when the process
+//     selects it (set_rpc_protocol("grpc") or TORCHFT_B200_RPC=grpc).
 #pragma once
 
 #include <atomic>
@@ -87,12 +90,22 @@ std::string local_hostname();
 int listen_on(const std::string& bind, int* port_out);                 // throws std::runtime_error
 int connect_to(const HostPort& hp, Millis timeout, std::string* err);  // -1 on failure
 
+// ---- blocking I/O with a deadline (poll based; `stopping` aborts a read early)
+enum IoResult { kIoOk, kIoTimeout, kIoClosed };
+IoResult read_exact(int fd, char* buf, size_t n, Clock::time_point deadline, const std::atomic<bool>* stopping);
+IoResult write_all(int fd, const char* buf, size_t n, Clock::time_point deadline);
+
+// ---- wire protocol used by Client objects of this process: "framed" (default) or "grpc"
+void set_rpc_protocol(const std::string& name);  // throws std::invalid_argument
+std::string rpc_protocol();
+
 // ---- server
 struct CallContext {
   std::optional<std::chrono::nanoseconds> timeout;  // from the request header
   Clock::time_point deadline = Clock::time_point::max();
-  int fd = -1;
+  int fd = -1;  // framed transport: the connection (one call at a time); -1 on multiplexed transports
   const std::atomic<bool>* stopping = nullptr;
+  const std::atomic<bool>* stream_cancelled = nullptr;  // HTTP/2: set when the peer reset the stream or went away
   // True once the deadline passed, the peer hung up or the server is shutting down.
   bool cancelled() const;
 };
@@ -152,11 +165,14 @@ class Client {
  private:
   void ensure_connected();
   void close_fd();
+  std::string call_grpc(const std::string& path, const std::string& payload, std::optional<Millis> timeout);
   std::string addr_;
   HostPort hp_;
   Millis connect_timeout_;
   std::mutex mu_;
   int fd_ = -1;
+  bool grpc_ = false;                          // fixed at construction from rpc_protocol()
+  std::shared_ptr<void> h2_;                   // h2::ClientConnection, owns the socket in gRPC mode
 };
 
 void log_info(const std::string& module, const std::string& msg);

@@ -64,6 +64,7 @@ int main(int argc, char** argv) {
   const int ranks = argc > 2 ? std::atoi(argv[2]) : 2;
   const int rounds = argc > 3 ? std::atoi(argv[3]) : 24;
   net::set_log_enabled(false);
+  if (argc > 4) net::set_rpc_protocol(argv[4]);  // "framed" or "grpc": wire protocol of every client in here
 
   LighthouseOptions opt;
   opt.bind = "[::]:0";
