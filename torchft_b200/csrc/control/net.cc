@@ -138,7 +138,13 @@ void log_info(const std::string& module, const std::string& msg) {
   strftime(ts, sizeof(ts), "%Y-%m-%dT%H:%M:%S", &tmv);
   char line[128];
   snprintf(line, sizeof(line), "%s.%03d", ts, static_cast<int>(tv.tv_usec / 1000));
-  std::string out = std::string(line) + " - INFO - [" + module + "] " + msg + "\n";
+  // colour only when asked for (CLICOLOR_FORCE, as the reference's logger) and never into a pipe by default
+  static const bool colour = [] {
+    const char* v = std::getenv("CLICOLOR_FORCE");
+    return v != nullptr && std::string(v) != "0" && std::string(v) != "";
+  }();
+  const std::string level = colour ? "\x1b[32mINFO\x1b[0m" : "INFO";
+  std::string out = std::string(line) + " - " + level + " - [" + module + "] " + msg + "\n";
   ssize_t ignored = ::write(2, out.data(), out.size());
   (void)ignored;
 }
