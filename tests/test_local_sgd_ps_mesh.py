@@ -222,3 +222,44 @@ def test_managed_device_mesh_four_processes():
     port = probe.port
     del probe
     mp.spawn(_mesh_worker, args=(4, port), nprocs=4, join=True)
+
+
+def _fsdp_worker(rank, world, port):
+    """HSDP from stock FSDP2: shard dimension on a real gloo mesh, replicate dimension managed."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["RANK"] = str(rank)
+    os.environ["WORLD_SIZE"] = str(world)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor import DTensor
+
+    manager = Mock(spec=Manager)
+    manager._pg = ProcessGroupGloo()
+    manager.num_participants.return_value = 1
+    manager.errored.return_value = None
+    mesh = ft_init_device_mesh(
+        device_type="cpu", mesh_shape=(2, world), mesh_dim_names=("dp_replicate", "dp_shard"), replicate_dim=0, manager=manager
+    )
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    reference = [p.detach().clone() for p in model.parameters()]
+    fully_shard(model, mesh=mesh)
+    assert all(isinstance(p, DTensor) for p in model.parameters())
+    x = torch.randn(8, 16, generator=torch.Generator().manual_seed(rank))
+    model(x).sum().backward()
+    # the replicate-dimension reduction went through the manager's process group view
+    assert manager.wait_quorum.call_count >= 1
+    for p, ref in zip(model.parameters(), reference):
+        assert p.grad is not None and isinstance(p.grad, DTensor)
+        assert p.grad.to_local().numel() * world >= ref.numel()  # row-sharded over the shard dimension
+    dist.destroy_process_group()
+
+
+def test_fsdp2_over_managed_mesh_two_processes():
+    from torch.distributed import TCPStore
+
+    probe = TCPStore(host_name="127.0.0.1", port=0, is_master=True, wait_for_workers=False)
+    port = probe.port
+    del probe
+    mp.spawn(_fsdp_worker, args=(2, port), nprocs=2, join=True)

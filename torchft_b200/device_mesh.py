@@ -195,6 +195,11 @@ class ManagedDeviceMesh(DeviceMesh):
         coord.insert(self.replicate_dim, self._replicate_rank())
         return coord
 
+    @property
+    def _coordinate_on_dim(self) -> Optional[List[int]]:
+        # DTensor asks the mesh whether this rank is part of it through this private field
+        return self.get_coordinate()
+
     def get_all_groups(self) -> List[BaseProcessGroup]:
         raise NotImplementedError
 
