@@ -11,7 +11,6 @@ this model exists because the benchmark configurations name Llama-3-8B and 1B sh
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 

@@ -35,7 +35,7 @@ from torch.distributed.distributed_c10d import ReduceOp, Work
 from torch.futures import Future
 
 from torchft_b200.ops import _lib
-from torchft_b200.process_group import ProcessGroup, _DummyWork, create_store_client
+from torchft_b200.process_group import ProcessGroup, create_store_client
 
 logger = logging.getLogger(__name__)
 
