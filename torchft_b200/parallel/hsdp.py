@@ -14,8 +14,10 @@ fp32 AdamW moments exist only for that slice.  A training step is
 2. per unit: reduce-scatter of the gradients over the shard group, then the allreduce of
    the owned slice over the replica groups (through the ``Manager``: averaged over the
    participating replicas, errors recorded instead of raised),
-3. ``Manager.should_commit()``; if it passes, fused AdamW on the owned slices; the updated
-   slices are all-gathered at the start of the next step.
+3. ``Manager.should_commit()``; if it passes, fused AdamW on the owned slices, unit by unit in
+   forward order on a stream of its own; the updated slices are all-gathered at the start of
+   the next step, and the next forward waits unit by unit.  The optimizer is bound by HBM
+   bandwidth and the forward pass by the tensor cores, so the two overlap well.
 
 Steps 2 and 3 use the NVLink peer-memory kernels of ``torchft_b200.parallel.nvlink`` when a
 shard communicator is given; with a single GPU per replica group they reduce to the
@@ -29,6 +31,7 @@ B200-first path used by ``bench.py``.
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Tuple
 
@@ -126,6 +129,9 @@ class HSDPEngine:
         self.exp_avg_sq = alloc(self.shard_total, torch.float32)
         # communication of finished units overlaps the rest of the backward pass on this stream
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        # the optimizer runs here so that the next step's forward can start while it still works
+        self.opt_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
+        self._updated: Dict[str, "torch.cuda.Event"] = {}
         self._by_name = {u.name: u for u in self.units}
         self._synced: set = set()
         self._futures: list = []
@@ -197,16 +203,35 @@ class HSDPEngine:
         torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
 
     def optimizer_step(self, grad_scale: float = 1.0) -> None:
-        """Fused AdamW on the owned slices (the next step starts by all-gathering them)."""
+        """Fused AdamW on the owned slices (the next step starts by all-gathering them).
+
+        With a model that announces its units in forward (``unit_pre_forward``) the kernels go to
+        the optimizer stream and every unit gets an event; otherwise they run on the calling stream.
+        """
         self.opt_step += 1
         b1, b2 = self.betas
-        for u in self.units:
-            F.adamw_step_(
-                self._own(self.flat_param, u), self._own(self.flat_grad, u),
-                self._state_slice(self.exp_avg, u), self._state_slice(self.exp_avg_sq, u),
-                lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=self.weight_decay,
-                step=self.opt_step, grad_scale=grad_scale,
-            )
+        current = torch.cuda.current_stream(self.device) if self.opt_stream is not None else None
+        side = self.opt_stream if self._prefetch else None
+        if side is not None:
+            side.wait_stream(current)  # gradients are final on the calling stream
+        ctx = torch.cuda.stream(side) if side is not None else contextlib.nullcontext()
+        with ctx:
+            for u in self.units:
+                F.adamw_step_(
+                    self._own(self.flat_param, u), self._own(self.flat_grad, u),
+                    self._state_slice(self.exp_avg, u), self._state_slice(self.exp_avg_sq, u),
+                    lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=self.weight_decay,
+                    step=self.opt_step, grad_scale=grad_scale,
+                )
+                if side is not None:
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                    self._updated[u.name] = ev
+
+    def wait_optimizer(self) -> None:
+        """Host-side wait until the optimizer kernels in flight are done (state is final afterwards)."""
+        if self.opt_stream is not None:
+            self.opt_stream.synchronize()
 
     def gather_parameters(self, overlap: bool = False) -> None:
         """All-gathers the owned parameter slices of every unit inside the replica group.
@@ -215,31 +240,42 @@ class HSDPEngine:
         ``unit_pre_forward`` callback makes the compute stream wait unit by unit; otherwise the
         calling stream sees all parameters complete when this returns.
         """
-        if self.comm.world == 1:
-            return
+        current = torch.cuda.current_stream(self.device) if self.comm_stream is not None else None
         if not (overlap and self._prefetch):
-            for u in self.units:
-                self.comm.all_gather_(self.flat_param[u.offset : u.offset + u.numel], self._shard_numel(u))
+            if self._updated:  # optimizer work of the previous step may still be in flight on its stream
+                current.wait_stream(self.opt_stream)
+                self._updated.clear()
+            if self.comm.world > 1:
+                for u in self.units:
+                    self.comm.all_gather_(self.flat_param[u.offset : u.offset + u.numel], self._shard_numel(u))
             return
-        current = torch.cuda.current_stream(self.device)
-        self.comm_stream.wait_stream(current)  # optimizer / recovery writes of the slices are ordered first
+        if self.comm.world == 1:
+            return  # forward waits for the optimizer events directly
+        self.comm_stream.wait_stream(current)  # recovery writes of the slices are ordered first
         with torch.cuda.stream(self.comm_stream):
             for u in self.units:
+                ev = self._updated.pop(u.name, None)
+                if ev is not None:
+                    self.comm_stream.wait_event(ev)  # this unit's slice has been updated
                 self.comm.all_gather_(self.flat_param[u.offset : u.offset + u.numel], self._shard_numel(u))
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
                 self._gathered[u.name] = ev
 
     def _unit_pre_forward(self, name: str) -> None:
-        ev = self._gathered.pop(name, None)
-        if ev is not None:
-            torch.cuda.current_stream(self.device).wait_event(ev)
+        for pending in (self._gathered, self._updated):
+            ev = pending.pop(name, None)
+            if ev is not None:
+                torch.cuda.current_stream(self.device).wait_event(ev)
 
     def _finish_gather(self) -> None:
         """Units whose forward did not run (or ran without the callback) are waited for here."""
         if self._gathered:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
             self._gathered.clear()
+        if self._updated:
+            torch.cuda.current_stream(self.device).wait_stream(self.opt_stream)
+            self._updated.clear()
 
     # ------------------------------------------------------------------ whole step
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -265,12 +301,14 @@ class HSDPEngine:
     def state_dict(self) -> Dict[str, object]:
         """State of THIS rank's slice; rank r of a recovering group pulls it from rank r of a healthy one."""
         # views, not copies: an NVLink transport moves them peer to peer without staging
+        self.wait_optimizer()  # whoever reads these views later, on whatever stream, sees final values
         own_params = [self._own(self.flat_param, u) for u in self.units]
         return {"params": own_params, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq, "opt_step": self.opt_step}
 
     def load_state_dict(self, sd: Dict[str, object]) -> None:
         params = sd["params"]
         assert isinstance(params, (list, tuple)) and len(params) == len(self.units)
+        self.wait_optimizer()  # nothing of an earlier step may still write the state
 
         def put(dst: torch.Tensor, src: torch.Tensor) -> None:
             # an in-place transport hands back our own tensors: nothing to copy then
