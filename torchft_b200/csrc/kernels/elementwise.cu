@@ -205,58 +205,6 @@ __global__ void adamw_kernel(__nv_bfloat16* __restrict__ p, const __nv_bfloat16*
   }
 }
 
-// Same update for a launch that shares the GPU with tensor-core kernels: few blocks per SM (so that
-// a persistent GEMM CTA still fits next to them) and two vectors in flight per thread to keep the
-// memory system busy at that low occupancy.  n must be a multiple of 8 (the caller guarantees it).
-__global__ void __launch_bounds__(256)
-adamw_shared_gpu_kernel(__nv_bfloat16* __restrict__ p, const __nv_bfloat16* __restrict__ g, float* __restrict__ m,
-                        float* __restrict__ v, long long n, float lr, float b1, float b2, float eps, float wd,
-                        float bc1, float bc2, float grad_scale) {
-  const long long nvec = n / 8;
-  const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  constexpr int UNR = 2;
-  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += stride * UNR) {
-    uint4 pv[UNR], gv[UNR];
-    float4 mv[UNR][2], vv[UNR][2];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const long long i = i0 + u * stride;
-      if (i < nvec) {
-        pv[u] = reinterpret_cast<const uint4*>(p)[i];
-        gv[u] = reinterpret_cast<const uint4*>(g)[i];
-        mv[u][0] = reinterpret_cast<const float4*>(m)[2 * i];
-        mv[u][1] = reinterpret_cast<const float4*>(m)[2 * i + 1];
-        vv[u][0] = reinterpret_cast<const float4*>(v)[2 * i];
-        vv[u][1] = reinterpret_cast<const float4*>(v)[2 * i + 1];
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const long long i = i0 + u * stride;
-      if (i >= nvec) break;
-      float pf[8], gf[8];
-      ew_unpack8(pv[u], pf);
-      ew_unpack8(gv[u], gf);
-      float mf[8] = {mv[u][0].x, mv[u][0].y, mv[u][0].z, mv[u][0].w, mv[u][1].x, mv[u][1].y, mv[u][1].z, mv[u][1].w};
-      float vf[8] = {vv[u][0].x, vv[u][0].y, vv[u][0].z, vv[u][0].w, vv[u][1].x, vv[u][1].y, vv[u][1].z, vv[u][1].w};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float gr = gf[j] * grad_scale;
-        mf[j] = b1 * mf[j] + (1.f - b1) * gr;
-        vf[j] = b2 * vf[j] + (1.f - b2) * gr * gr;
-        const float denom = sqrtf(vf[j]) * inv_sqrt_bc2 + eps;
-        pf[j] = pf[j] * (1.f - lr * wd) - lr * (mf[j] * inv_bc1) / denom;
-      }
-      reinterpret_cast<uint4*>(p)[i] = ew_pack8(pf);
-      reinterpret_cast<float4*>(m)[2 * i] = make_float4(mf[0], mf[1], mf[2], mf[3]);
-      reinterpret_cast<float4*>(m)[2 * i + 1] = make_float4(mf[4], mf[5], mf[6], mf[7]);
-      reinterpret_cast<float4*>(v)[2 * i] = make_float4(vf[0], vf[1], vf[2], vf[3]);
-      reinterpret_cast<float4*>(v)[2 * i + 1] = make_float4(vf[4], vf[5], vf[6], vf[7]);
-    }
-  }
-}
-
 // ------------------------------------------------------------------ DiLoCo outer step
 template <typename T>
 __device__ __forceinline__ float ld1(const T* p, long long i);
@@ -362,24 +310,6 @@ TFT_API int tft_adamw(void* p, const void* g, float* m, float* v, long long n, f
   adamw_kernel<<<ew_grid(n / 8 + 8, 256), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p),
                                                             static_cast<const __nv_bfloat16*>(g), m, v, n, lr, b1,
                                                             b2, eps, wd, bc1, bc2, grad_scale);
-  return static_cast<int>(cudaGetLastError());
-}
-
-// AdamW for a stream that runs beside tensor-core work: at most `max_blocks` blocks of 256 threads.
-// n must be a multiple of 8.
-TFT_API int tft_adamw_shared_gpu(void* p, const void* g, float* m, float* v, long long n, float lr, float b1, float b2,
-                                 float eps, float wd, int step, float grad_scale, int max_blocks, cudaStream_t stream) {
-  if (n <= 0) return 0;
-  if (n % 8 || max_blocks < 1) return static_cast<int>(cudaErrorInvalidValue);
-  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) return static_cast<int>(cudaErrorInvalidValue);
-  if ((reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) return static_cast<int>(cudaErrorInvalidValue);
-  const float bc1 = 1.f - powf(b1, static_cast<float>(step));
-  const float bc2 = 1.f - powf(b2, static_cast<float>(step));
-  long long blocks = (n / 8 + 511) / 512;
-  if (blocks > max_blocks) blocks = max_blocks;
-  adamw_shared_gpu_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p),
-                                                                         static_cast<const __nv_bfloat16*>(g), m, v, n, lr,
-                                                                         b1, b2, eps, wd, bc1, bc2, grad_scale);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -35,7 +35,6 @@ _PROTOTYPES = {
     "tft_embedding_fwd": [P, P, P, L, I, P],
     "tft_embedding_bwd": [P, P, P, L, I, P],
     "tft_adamw": [P, P, P, P, L, F, F, F, F, F, I, F, P],
-    "tft_adamw_shared_gpu": [P, P, P, P, L, F, F, F, F, F, I, F, I, P],
     "tft_pseudograd": [P, P, L, I, P],
     "tft_nesterov_outer": [P, P, P, L, F, F, I, I, I, P],
     "tft_attn_fwd": [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],

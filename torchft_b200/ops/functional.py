@@ -308,22 +308,13 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------------ AdamW
 def adamw_step_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *, lr: float, beta1: float,
-                beta2: float, eps: float, weight_decay: float, step: int, grad_scale: float = 1.0,
-                max_blocks: Optional[int] = None) -> None:
-    """One fused AdamW update of a flat bf16 parameter buffer with fp32 moments.
-
-    ``max_blocks`` caps the grid (blocks of 256 threads) for launches that run beside tensor-core
-    kernels on another stream, so that those still find room on every SM.
-    """
+                beta2: float, eps: float, weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
+    """One fused AdamW update of a flat bf16 parameter buffer with fp32 moments."""
     assert p.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and m.dtype == torch.float32 and v.dtype == torch.float32
     assert p.is_contiguous() and g.is_contiguous() and m.is_contiguous() and v.is_contiguous()
     n = p.numel()
     assert g.numel() == n and m.numel() == n and v.numel() == n
-    if max_blocks is not None and n % 8 == 0:
-        code = _lib.lib().tft_adamw_shared_gpu(_lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), n, lr, beta1, beta2,
-                                               eps, weight_decay, step, grad_scale, max_blocks, _lib.stream_ptr())
-    else:
-        code = _lib.lib().tft_adamw(_lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), n, lr, beta1, beta2, eps,
-                                    weight_decay, step, grad_scale, _lib.stream_ptr())
+    code = _lib.lib().tft_adamw(_lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), n, lr, beta1, beta2, eps,
+                                weight_decay, step, grad_scale, _lib.stream_ptr())
     _lib.check(code, "tft_adamw")
     _lib.count_launch()

@@ -132,8 +132,6 @@ class HSDPEngine:
         # the optimizer runs here so that the next step's forward can start while it still works
         self.opt_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self._updated: Dict[str, "torch.cuda.Event"] = {}
-        self.opt_blocks = 2 * (torch.cuda.get_device_properties(self.device).multi_processor_count
-                               if self.device.type == "cuda" else 1)
         self._by_name = {u.name: u for u in self.units}
         self._synced: set = set()
         self._futures: list = []
@@ -224,8 +222,6 @@ class HSDPEngine:
                     self._state_slice(self.exp_avg, u), self._state_slice(self.exp_avg_sq, u),
                     lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=self.weight_decay,
                     step=self.opt_step, grad_scale=grad_scale,
-                    # beside the next forward: two blocks per SM leave room for a GEMM CTA on each
-                    max_blocks=self.opt_blocks if side is not None else None,
                 )
                 if side is not None:
                     ev = torch.cuda.Event()
