@@ -346,3 +346,87 @@ def test_protocol_switch_validation():
     with pytest.raises(ValueError):
         C.set_rpc_protocol("carrier-pigeon")
     assert C.rpc_protocol() in ("framed", "grpc")
+
+
+# ---------------------------------------------------------------- hand-made frames
+def _frame(ftype, flags, stream, payload=b""):
+    n = len(payload)
+    return bytes([(n >> 16) & 255, (n >> 8) & 255, n & 255, ftype, flags]) + stream.to_bytes(4, "big") + payload
+
+
+def _read_frames(sock, until_end_of_stream):
+    """Reads frames until the given stream carries END_STREAM; returns [(type, flags, stream, payload)]."""
+    out, buf = [], b""
+    sock.settimeout(10)
+    while True:
+        while len(buf) < 9:
+            chunk = sock.recv(65536)
+            assert chunk, "server closed the connection"
+            buf += chunk
+        n = int.from_bytes(buf[:3], "big")
+        while len(buf) < 9 + n:
+            chunk = sock.recv(65536)
+            assert chunk, "server closed the connection"
+            buf += chunk
+        ftype, flags, stream = buf[3], buf[4], int.from_bytes(buf[5:9], "big") & 0x7FFFFFFF
+        out.append((ftype, flags, stream, buf[9 : 9 + n]))
+        buf = buf[9 + n :]
+        if stream == until_end_of_stream and ftype in (0, 1) and flags & 0x1:
+            return out
+
+
+def test_continuation_padding_priority_and_split_data():
+    """Frame layouts a gRPC library rarely produces: header block in HEADERS + CONTINUATION with
+    padding and a priority block, message split over two DATA frames (one padded), PING in between."""
+    import socket
+
+    S = _schema()
+    lighthouse = C.Lighthouse(bind="[::]:0", min_replicas=1, join_timeout_ms=100, quorum_tick_ms=10)
+    try:
+        port = int(lighthouse.address().rsplit(":", 1)[1])
+        sock = socket.create_connection(("127.0.0.1", port))
+        sock.sendall(b"PRI * HTTP/2.0\r\n\r\nSM\r\n\r\n" + _frame(4, 0, 0))
+        block = C.hpack_encode([(":method", "POST"), (":scheme", "http"), (":path", "/torchft.LighthouseService/Quorum"),
+                                (":authority", "x"), ("te", "trailers"), ("content-type", "application/grpc"),
+                                ("grpc-timeout", "5S")], True)
+        cut = len(block) // 2
+        pad = 7
+        headers = bytes([pad]) + b"\x00\x00\x00\x00\x10" + block[:cut] + bytes(pad)  # PADDED | PRIORITY
+        sock.sendall(_frame(1, 0x08 | 0x20, 1, headers) + _frame(9, 0x4, 1, block[cut:]))
+        member = S.QuorumMember(replica_id="raw", address="a", store_address="s", step=2, world_size=1)
+        message = S.LighthouseQuorumRequest(requester=member).SerializeToString()
+        body = b"\x00" + len(message).to_bytes(4, "big") + message
+        half = len(body) // 2
+        sock.sendall(_frame(0, 0x08, 1, bytes([3]) + body[:half] + bytes(3)) + _frame(6, 0, 0, b"12345678") +
+                     _frame(0, 0x1, 1, body[half:]))
+        frames = _read_frames(sock, until_end_of_stream=1)
+        assert any(t == 6 and f & 0x1 and p == b"12345678" for t, f, s, p in frames), "PING was not acknowledged"
+        assert any(t == 4 and f & 0x1 for t, f, s, p in frames), "SETTINGS was not acknowledged"
+        decoder = C.HpackDecoder()
+        blocks = [decoder.decode(p) for t, f, s, p in frames if t == 1 and s == 1]
+        assert dict(blocks[0])[b":status"] == b"200" and dict(blocks[0])[b"content-type"] == b"application/grpc"
+        assert dict(blocks[-1])[b"grpc-status"] == b"0"
+        data = b"".join(p for t, f, s, p in frames if t == 0 and s == 1)
+        assert data[0] == 0 and int.from_bytes(data[1:5], "big") == len(data) - 5
+        resp = S.LighthouseQuorumResponse.FromString(data[5:])
+        assert [p.replica_id for p in resp.quorum.participants] == ["raw"]
+        # flow control: the server returned the DATA bytes it consumed to the connection window
+        credited = sum(int.from_bytes(p, "big") for t, f, s, p in frames if t == 8 and s == 0)
+        assert credited == len(body) + 1 + 3  # both DATA payloads, the pad-length byte and the padding included
+
+        # an even stream id from a client is a protocol error: GOAWAY
+        sock.sendall(_frame(1, 0x4 | 0x1, 2, block))
+        sock.settimeout(5)
+        tail = b""
+        try:
+            while True:
+                chunk = sock.recv(4096)
+                if not chunk:
+                    break
+                tail += chunk
+        except OSError:
+            pass
+        assert len(tail) >= 9 and tail[3] == 7, "expected a GOAWAY frame"
+        sock.close()
+    finally:
+        lighthouse.shutdown()
