@@ -380,7 +380,9 @@ enum FrameType : uint8_t {
 };
 constexpr uint8_t kFlagEndStream = 0x1, kFlagAck = 0x1, kFlagEndHeaders = 0x4, kFlagPadded = 0x8, kFlagPriority = 0x20;
 constexpr uint16_t kSettingsHeaderTableSize = 1, kSettingsInitialWindowSize = 4, kSettingsMaxFrameSize = 5;
-constexpr uint32_t kErrProtocol = 1, kErrCancel = 8, kErrCompression = 9;
+constexpr uint32_t kErrProtocol = 1, kErrRefusedStream = 7, kErrCancel = 8, kErrCompression = 9;
+constexpr size_t kMaxOpenStreams = 1024;  // calls in progress per connection (advertised in SETTINGS)
+constexpr uint16_t kSettingsMaxConcurrentStreams = 3;
 const char kPreface[] = "PRI * HTTP/2.0\r\n\r\nSM\r\n\r\n";
 constexpr size_t kPrefaceLen = 24;
 constexpr uint32_t kMaxMessageBytes = 64u << 20;
@@ -588,7 +590,13 @@ void serve_connection(int fd, const std::string& prefix, const std::atomic<bool>
   auto conn = std::make_shared<ServerConn>();
   conn->fd = fd;
   conn->stopping = &stopping;
-  if (!conn->send(frame_bytes(kSettings, 0, 0, ""))) return;
+  {
+    std::string settings;
+    settings.push_back(static_cast<char>(kSettingsMaxConcurrentStreams >> 8));
+    settings.push_back(static_cast<char>(kSettingsMaxConcurrentStreams & 0xff));
+    settings.append(u32_bytes(static_cast<uint32_t>(kMaxOpenStreams)));
+    if (!conn->send(frame_bytes(kSettings, 0, 0, settings))) return;
+  }
 
   HpackDecoder decoder;
   uint32_t continuation_stream = 0;  // non-zero while a header block is open
@@ -761,6 +769,12 @@ void serve_connection(int fd, const std::string& prefix, const std::atomic<bool>
       bool ready = false;
       {
         std::lock_guard<std::mutex> g(conn->mu);
+        if (conn->streams.size() > kMaxOpenStreams) {
+          // the block had to be decoded (the compression state is per connection); the call is refused
+          conn->streams.erase(id);
+          conn->send_locked(frame_bytes(kRstStream, 0, id, u32_bytes(kErrRefusedStream)));
+          continue;
+        }
         ServerStream& s = conn->streams[id];
         if (!s.headers_done) {
           s.headers = decoded;
