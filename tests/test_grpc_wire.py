@@ -430,3 +430,39 @@ def test_continuation_padding_priority_and_split_data():
         sock.close()
     finally:
         lighthouse.shutdown()
+
+
+def test_server_survives_garbage_frames():
+    """Random frames after a valid preface must at worst close that connection, never the server."""
+    import random
+    import socket
+
+    S = _schema()
+    lighthouse = C.Lighthouse(bind="[::]:0", min_replicas=1, join_timeout_ms=100, quorum_tick_ms=10)
+    try:
+        port = int(lighthouse.address().rsplit(":", 1)[1])
+        rng = random.Random(1234)
+        for conn in range(20):
+            sock = socket.create_connection(("127.0.0.1", port))
+            sock.settimeout(2)
+            try:
+                sock.sendall(b"PRI * HTTP/2.0\r\n\r\nSM\r\n\r\n" + _frame(4, 0, 0))
+                for _ in range(rng.randint(1, 30)):
+                    payload = bytes(rng.getrandbits(8) for _ in range(rng.randint(0, 64)))
+                    stream = rng.choice([0, 1, 1, 3, 5, 2, 2**31 - 1])
+                    sock.sendall(_frame(rng.randint(0, 11), rng.getrandbits(8), stream, payload))
+                if conn % 3 == 0:
+                    sock.sendall(bytes(rng.getrandbits(8) for _ in range(100)))  # not even frames
+            except OSError:
+                pass  # the server hung up on a protocol error: fine
+            finally:
+                sock.close()
+        # truncated preface and a preface with a wrong tail
+        for bad in (b"PRI * HT", b"PRI * HTTP/2.0\r\n\r\nXX\r\n\r\n"):
+            sock = socket.create_connection(("127.0.0.1", port))
+            sock.sendall(bad)
+            sock.close()
+        with grpc.insecure_channel(f"127.0.0.1:{port}") as ch:
+            _unary(ch, "/torchft.LighthouseService/Heartbeat", S.LighthouseHeartbeatRequest(replica_id="after"), S.Empty)
+    finally:
+        lighthouse.shutdown()

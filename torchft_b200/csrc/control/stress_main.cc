@@ -57,6 +57,49 @@ std::string http_get(int port, const std::string& path) {
   return out;
 }
 
+// Connects like an HTTP/2 client and then sends random frames: the server may drop the connection,
+// it must not misbehave (the sanitizers watch the parser).
+void garbage_client(int port, unsigned seed) {
+  std::string err;
+  net::HostPort hp{"127.0.0.1", port};
+  const int fd = net::connect_to(hp, Millis(2000), &err);
+  if (fd < 0) return;
+  std::string out = "PRI * HTTP/2.0\r\n\r\nSM\r\n\r\n";
+  out += std::string("\0\0\0\4\0\0\0\0\0", 9);  // empty SETTINGS
+  unsigned state = seed * 2654435761u + 1;
+  auto next = [&state] {
+    state = state * 1664525u + 1013904223u;
+    return state >> 8;
+  };
+  const int frames = 1 + static_cast<int>(next() % 40);
+  for (int i = 0; i < frames; ++i) {
+    const unsigned len = next() % 80;
+    const unsigned streams[] = {0, 1, 1, 3, 5, 2, 0x7fffffffu};
+    const unsigned stream = streams[next() % 7];
+    out.push_back(0);
+    out.push_back(0);
+    out.push_back(static_cast<char>(len));
+    out.push_back(static_cast<char>(next() % 12));
+    out.push_back(static_cast<char>(next() & 0xff));
+    out.push_back(static_cast<char>((stream >> 24) & 0x7f));
+    out.push_back(static_cast<char>((stream >> 16) & 0xff));
+    out.push_back(static_cast<char>((stream >> 8) & 0xff));
+    out.push_back(static_cast<char>(stream & 0xff));
+    for (unsigned j = 0; j < len; ++j) out.push_back(static_cast<char>(next() & 0xff));
+  }
+  size_t sent = 0;
+  while (sent < out.size()) {
+    const ssize_t n = ::send(fd, out.data() + sent, out.size() - sent, MSG_NOSIGNAL);
+    if (n <= 0) break;
+    sent += static_cast<size_t>(n);
+  }
+  ::shutdown(fd, SHUT_WR);
+  char buf[4096];
+  while (::recv(fd, buf, sizeof(buf), 0) > 0) {
+  }
+  ::close(fd);
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -82,10 +125,12 @@ int main(int argc, char** argv) {
                                                        Millis(20), Millis(5000)));
 
   std::atomic<bool> stop_dashboard{false};
+  unsigned garbage_seed = 1;
   std::thread dashboard([&] {
     while (!stop_dashboard.load()) {
       const std::string page = http_get(lighthouse->port(), "/status");
       if (!page.empty() && page.find("200") == std::string::npos) fail("dashboard did not answer 200");
+      garbage_client(lighthouse->port(), garbage_seed++);
       std::this_thread::sleep_for(Millis(3));
     }
   });
