@@ -48,6 +48,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama_1b", "tiny"])
     ap.add_argument("--seq", type=int, default=0, help="sequence length (default: the model's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="shard every projection matrix by rows and gather it inside its first GEMM of the step "
+                         "(all-gather fused GEMM) instead of with separate all-gather kernels")
     return ap.parse_args()
 
 
@@ -204,9 +207,13 @@ def run_ours(args: argparse.Namespace) -> None:
         # step-0 weight sync and any later recovery move GPU to GPU over NVLink
         checkpoint_transport=NVLinkCheckpointTransport(heap, timeout=timedelta(seconds=120)),
     )
+    fused = None
+    if args.fused_gather and shard_world > 1:
+        fused = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
+        fused.configure(PrefixStore("fused", client_store), shard_rank, shard_world, f"fused-group-{group}")
     engine = HSDPEngine(
-        model, model.units(), manager=manager, shard_comm=NVLinkShardComm(shard),
-        lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc,
+        model, model.units(per_weight=fused is not None), manager=manager, shard_comm=NVLinkShardComm(shard),
+        lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,
     )
     engine_box["engine"] = engine
 

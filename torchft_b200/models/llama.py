@@ -172,12 +172,23 @@ class Llama(nn.Module):
             self._cs = F.rope_table(self.cfg.max_seq_len, self.cfg.head_dim, self.cfg.rope_theta, device)
         return self._cs
 
-    def units(self) -> List[Tuple[str, List[nn.Parameter]]]:
+    def units(self, per_weight: bool = False) -> List[Tuple[str, List[nn.Parameter]]]:
         """Parameters grouped the way they are sharded and communicated: the embedding, one
-        group per block, and the head (final norm + output projection)."""
+        group per block, and the head (final norm + output projection).
+
+        With ``per_weight`` every projection matrix of a block is a unit of its own, named
+        ``layer<i>/<weight>`` (the norms of the block share ``layer<i>/norms``); an engine that
+        shards by unit then shards each matrix by rows, which is what the all-gather fused into
+        the GEMM needs.  Callbacks keep using the block name ``layer<i>`` as a prefix.
+        """
         groups: List[Tuple[str, List[nn.Parameter]]] = [("embed", [self.tok_embeddings])]
         for i, layer in enumerate(self.layers):
-            groups.append((f"layer{i}", list(layer.parameters())))
+            if per_weight:
+                for wname in ("wqkv", "wo", "w13", "w2"):
+                    groups.append((f"layer{i}/{wname}", [getattr(layer, wname)]))
+                groups.append((f"layer{i}/norms", [layer.attn_norm, layer.ffn_norm]))
+            else:
+                groups.append((f"layer{i}", list(layer.parameters())))
         groups.append(("head", [self.norm, self.output]))
         return groups
 

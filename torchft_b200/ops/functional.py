@@ -28,12 +28,25 @@ class _Linear(torch.autograd.Function):
     example a slice of a flat gradient bucket), the weight gradient is written or
     accumulated there directly and autograd sees ``None`` for it; the flag
     ``main_grad_initialized`` tells whether to overwrite or accumulate.
+
+    If the weight carries ``gather_comm`` (an ``NVLinkCommunicator``) and ``gather_pending`` is
+    set, the forward product runs through the all-gather fused GEMM, which also completes the
+    local copy of the weight for the backward products.
     """
 
     @staticmethod
     def forward(ctx, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
+        comm = getattr(w, "gather_comm", None)
+        if comm is not None and getattr(w, "gather_pending", False):
+            # the weight is sharded by rows over the GPUs of the group and only this rank's rows are
+            # current: ONE kernel pulls the peers' rows into place and multiplies as they arrive
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+            y = comm.all_gather_linear(x2, w)
+            w.gather_pending = False
+        else:
+            y = gemm(x2, w)
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.weight = w

@@ -49,6 +49,7 @@ class Unit:
     params: List[nn.Parameter]
     offset: int  # start inside the flat buffers (elements)
     numel: int  # padded length (multiple of ALIGN * shard_world)
+    fused_gather: bool = False  # its all-gather happens inside the GEMM that first uses it
 
 
 class ShardComm:
@@ -77,6 +78,7 @@ class HSDPEngine:
         eps: float = 1e-8,
         weight_decay: float = 0.1,
         alloc: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None,
+        fused_gather_comm=None,
     ) -> None:
         """
         Args:
@@ -85,6 +87,10 @@ class HSDPEngine:
             shard_comm: collectives of the shard dimension (``None``: one GPU per group)
             alloc: allocator for the flat buffers, ``alloc(numel, dtype) -> tensor``; the
                 NVLink backend passes its symmetric-heap allocator so peers can address them
+            fused_gather_comm: an ``NVLinkCommunicator`` of the shard group (a channel of its own).
+                Units that consist of ONE matrix ``[N, K]`` with ``N % (256 * shard_world) == 0`` and
+                ``K % 64 == 0`` (``Llama.units(per_weight=True)``) then skip the all-gather kernel:
+                their rows are gathered inside the first GEMM that uses the weight in a step
         """
         self.model = model
         self.manager = manager
@@ -133,6 +139,21 @@ class HSDPEngine:
         self.opt_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self._updated: Dict[str, "torch.cuda.Event"] = {}
         self._by_name = {u.name: u for u in self.units}
+        # callbacks name a block ("layer3"); its units are "layer3" itself or "layer3/<part>"
+        self._by_prefix: Dict[str, List[Unit]] = {}
+        for u in self.units:
+            self._by_prefix.setdefault(u.name.split("/", 1)[0], []).append(u)
+        self._fused_units: List[Unit] = []
+        if fused_gather_comm is not None and S > 1:
+            for u in self.units:
+                if len(u.params) != 1 or u.params[0].dim() != 2:
+                    continue
+                n_rows, k = u.params[0].shape
+                if n_rows % (256 * S) == 0 and k % 64 == 0 and u.numel == n_rows * k:
+                    u.fused_gather = True
+                    u.params[0].gather_comm = fused_gather_comm
+                    u.params[0].gather_pending = False
+                    self._fused_units.append(u)
         self._synced: set = set()
         self._futures: list = []
         if hasattr(model, "unit_grad_ready"):
@@ -184,9 +205,8 @@ class HSDPEngine:
                 self._futures.append(self.manager.allreduce(self._own(self.flat_grad, u)))
 
     def _unit_grad_ready(self, name: str) -> None:
-        """Backward-time callback of the model: the named unit's gradients are final."""
-        u = self._by_name.get(name)
-        if u is not None:
+        """Backward-time callback of the model: the gradients of the named block's units are final."""
+        for u in reversed(self._by_prefix.get(name, ())):
             self._sync_unit(u)
 
     def sync_gradients(self) -> None:
@@ -251,9 +271,13 @@ class HSDPEngine:
             return
         if self.comm.world == 1:
             return  # forward waits for the optimizer events directly
+        for u in self._fused_units:
+            u.params[0].gather_pending = True  # gathered by the GEMM that uses the weight first
         self.comm_stream.wait_stream(current)  # recovery writes of the slices are ordered first
         with torch.cuda.stream(self.comm_stream):
             for u in self.units:
+                if u.fused_gather:
+                    continue  # its optimizer event stays in _updated: forward waits for it directly
                 ev = self._updated.pop(u.name, None)
                 if ev is not None:
                     self.comm_stream.wait_event(ev)  # this unit's slice has been updated
@@ -263,10 +287,11 @@ class HSDPEngine:
                 self._gathered[u.name] = ev
 
     def _unit_pre_forward(self, name: str) -> None:
-        for pending in (self._gathered, self._updated):
-            ev = pending.pop(name, None)
-            if ev is not None:
-                torch.cuda.current_stream(self.device).wait_event(ev)
+        for u in self._by_prefix.get(name, ()):
+            for pending in (self._gathered, self._updated):
+                ev = pending.pop(u.name, None)
+                if ev is not None:
+                    torch.cuda.current_stream(self.device).wait_event(ev)
 
     def _finish_gather(self) -> None:
         """Units whose forward did not run (or ran without the callback) are waited for here."""
