@@ -306,6 +306,8 @@ def run_ours(args: argparse.Namespace) -> None:
                 "parallelism": f"hsdp{n_groups}x{shard_world} (replica groups x shard GPUs)",
                 "optimizer": "fused AdamW lr 3e-4 betas (0.9, 0.95) wd 0.1, fp32 moments",
                 "quorum": "lighthouse quorum + should_commit every step",
+                "parameter_gather": ("inside the first GEMM of each projection (all-gather fused GEMM)" if fused is not None
+                                     else "per-unit all-gather kernels overlapped with forward"),
                 "l2_policy": "no flush needed: weights, gradients and activations streamed per step exceed 100 GB (L2 is 126 MB)",
             },
             "clocks": clocks,
