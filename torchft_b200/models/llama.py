@@ -120,6 +120,8 @@ class LlamaBlock(nn.Module):
         self.ffn_norm = nn.Parameter(torch.ones(cfg.dim, **kw))
         self.w13 = nn.Parameter(torch.empty(2 * cfg.ffn_dim, cfg.dim, **kw))
         self.w2 = nn.Parameter(torch.empty(cfg.dim, cfg.ffn_dim, **kw))
+        for w in (self.wqkv, self.wo, self.w13, self.w2):
+            w.linear_weight = True  # used only through F.linear: eligible for the all-gather fused GEMM
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], cs: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Takes the previous block's MLP output ``x`` and residual stream; returns the same pair."""

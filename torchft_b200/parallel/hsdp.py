@@ -88,7 +88,7 @@ class HSDPEngine:
             alloc: allocator for the flat buffers, ``alloc(numel, dtype) -> tensor``; the
                 NVLink backend passes its symmetric-heap allocator so peers can address them
             fused_gather_comm: an ``NVLinkCommunicator`` of the shard group (a channel of its own).
-                Units that consist of ONE matrix ``[N, K]`` with ``N % (256 * shard_world) == 0`` and
+                Units that consist of ONE matrix ``[N, K]`` marked ``linear_weight`` by the model, with ``N % (256 * shard_world) == 0`` and
                 ``K % 64 == 0`` (``Llama.units(per_weight=True)``) then skip the all-gather kernel:
                 their rows are gathered inside the first GEMM that uses the weight in a step
         """
@@ -146,8 +146,8 @@ class HSDPEngine:
         self._fused_units: List[Unit] = []
         if fused_gather_comm is not None and S > 1:
             for u in self.units:
-                if len(u.params) != 1 or u.params[0].dim() != 2:
-                    continue
+                if len(u.params) != 1 or u.params[0].dim() != 2 or not getattr(u.params[0], "linear_weight", False):
+                    continue  # only matrices that the model marks as used through F.linear alone
                 n_rows, k = u.params[0].shape
                 if n_rows % (256 * S) == 0 and k % 64 == 0 and u.numel == n_rows * k:
                     u.fused_gather = True
