@@ -19,3 +19,12 @@ __all__ = (
     "ProcessGroupBabyNCCL",
     "ProcessGroupGloo",
 )
+
+
+def __getattr__(name: str):
+    # resolved on first use: the NVLink backend pulls in the CUDA kernel library
+    if name == "ProcessGroupNVLink":
+        from torchft_b200.parallel.nvlink import ProcessGroupNVLink
+
+        return ProcessGroupNVLink
+    raise AttributeError(f"module 'torchft_b200' has no attribute {name!r}")
