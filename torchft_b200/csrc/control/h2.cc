@@ -550,9 +550,20 @@ void respond(ServerConn* c, uint32_t stream, const Status& st, const std::string
     c->streams.erase(stream);
     return;
   }
-  c->send_locked(frame_bytes(kHeaders, kFlagEndHeaders, stream,
-                             hpack_encode({{":status", "200"}, {"content-type", "application/grpc"}}, false)));
+  const std::string head = frame_bytes(kHeaders, kFlagEndHeaders, stream,
+                                       hpack_encode({{":status", "200"}, {"content-type", "application/grpc"}}, false));
   const std::string body = grpc_frame(message);
+  // common case: the whole message fits one frame and both windows, so headers, message and trailers
+  // leave in a single write
+  if (body.size() <= c->peer_max_frame && static_cast<int64_t>(body.size()) <= c->conn_send_window &&
+      static_cast<int64_t>(body.size()) <= it->second.send_window) {
+    c->conn_send_window -= static_cast<int64_t>(body.size());
+    c->send_locked(head + frame_bytes(kData, 0, stream, body) +
+                   frame_bytes(kHeaders, kFlagEndHeaders | kFlagEndStream, stream, hpack_encode(trailers, false)));
+    c->streams.erase(stream);
+    return;
+  }
+  c->send_locked(head);
   size_t off = 0;
   const Clock::time_point give_up = Clock::now() + std::chrono::seconds(60);
   while (off < body.size() && !c->dead.load()) {
