@@ -121,6 +121,7 @@ __device__ void copy_role(const Params& p, uint8_t* smem, uint32_t base, uint32_
     auto ring_bar = [&](int s) { return bar_base + 8u * s; };
     for (int s = 0; s < RING; ++s) mbar_init(ring_bar(s), 1);
     mbar_fence_init();
+    fence_proxy_async();  // the peers' rows were published to the generic proxy; the bulk copies read them through the async one
     volatile int local_abort = 0;
     auto locate = [&](long long i, const uint8_t** src, uint8_t** dst, uint32_t* bytes, int* blk) {
       const int rb = static_cast<int>(i / chunks_per_block);       // remote block in walk order
