@@ -397,3 +397,23 @@ def test_force_reconfigure_bumps_quorum_id_without_membership_change():
         for m in managers:
             m.shutdown()
         lh.shutdown()
+
+
+def test_wire_decoder_rejects_garbage_without_crashing():
+    """Random and truncated payloads end in an exception or a value, never in a crash."""
+    import random
+
+    rng = random.Random(7)
+    good = C.encode_quorum_member({"replica_id": "r", "address": "a", "store_address": "s", "step": 5, "world_size": 2, "shrink_only": False})
+    samples = [bytes(rng.getrandbits(8) for _ in range(rng.randint(0, 64))) for _ in range(500)]
+    samples += [good[:n] for n in range(len(good))]
+    samples += [b"\x0a\xff\xff\xff\xff\x0f" + b"x" * 10, b"\xff" * 32, b"\x08" + b"\x80" * 20]
+    outcomes = {"ok": 0, "error": 0}
+    for payload in samples:
+        for decode in (C.decode_quorum_member, C.decode_manager_quorum_response):
+            try:
+                decode(payload)
+                outcomes["ok"] += 1
+            except (RuntimeError, ValueError):
+                outcomes["error"] += 1
+    assert outcomes["error"] > 0 and outcomes["ok"] > 0
