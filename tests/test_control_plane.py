@@ -242,6 +242,9 @@ def test_dashboard_http():
         assert "dash" in status and "Step: 7" in status and "Heartbeats" in status
         js = urllib.request.urlopen(lh.address() + "/status.json").read().decode()
         assert '"quorum_id": 1' in js
+        metrics = urllib.request.urlopen(lh.address() + "/metrics").read().decode()
+        assert "torchft_quorum_id 1" in metrics and "torchft_quorum_participants 1" in metrics
+        assert 'torchft_replica_step{replica_id="dash' in metrics and "torchft_heartbeat_age_seconds{" in metrics
         req = urllib.request.Request(lh.address() + "/replica/unknown/kill", method="POST")
         with pytest.raises(urllib.error.HTTPError) as ei:
             urllib.request.urlopen(req)

@@ -275,6 +275,36 @@ net::HttpResponse Lighthouse::handle_http(const net::HttpRequest& req) {
     resp.body = o.str();
     return resp;
   }
+  if (req.method == "GET" && req.path == "/metrics") {
+    // Prometheus text exposition format
+    std::lock_guard<std::mutex> g(mu_);
+    const auto now = net::Clock::now();
+    std::ostringstream o;
+    o << "# HELP torchft_quorum_id Identifier of the current quorum (changes with membership).\n"
+      << "# TYPE torchft_quorum_id gauge\ntorchft_quorum_id " << state_.quorum_id << "\n"
+      << "# HELP torchft_quorums_published_total Quorums handed out since start.\n"
+      << "# TYPE torchft_quorums_published_total counter\ntorchft_quorums_published_total " << seq_ << "\n"
+      << "# HELP torchft_quorum_participants Members of the current quorum.\n"
+      << "# TYPE torchft_quorum_participants gauge\ntorchft_quorum_participants "
+      << (state_.prev_quorum ? state_.prev_quorum->participants.size() : 0) << "\n"
+      << "# HELP torchft_waiting_participants Replica groups waiting for the next quorum.\n"
+      << "# TYPE torchft_waiting_participants gauge\ntorchft_waiting_participants " << state_.participants.size() << "\n"
+      << "# HELP torchft_heartbeat_age_seconds Time since the last heartbeat of a replica group.\n"
+      << "# TYPE torchft_heartbeat_age_seconds gauge\n";
+    for (const auto& kv : state_.heartbeats) {
+      const double age = std::chrono::duration<double>(now - kv.second).count();
+      o << "torchft_heartbeat_age_seconds{replica_id=\"" << json_escape(kv.first) << "\"} " << age << "\n";
+    }
+    if (state_.prev_quorum) {
+      o << "# HELP torchft_replica_step Step reported by a member when the current quorum formed.\n"
+        << "# TYPE torchft_replica_step gauge\n";
+      for (const auto& m : state_.prev_quorum->participants)
+        o << "torchft_replica_step{replica_id=\"" << json_escape(m.replica_id) << "\"} " << m.step << "\n";
+    }
+    resp.content_type = "text/plain; version=0.0.4";
+    resp.body = o.str();
+    return resp;
+  }
   const std::string prefix = "/replica/";
   const std::string suffix = "/kill";
   if (req.method == "POST" && req.path.compare(0, prefix.size(), prefix) == 0 && req.path.size() > prefix.size() + suffix.size() &&
