@@ -73,7 +73,11 @@ inline bool make_attn_tensormap(CUtensorMap* out, const void* ptr, int hd, int h
                            static_cast<cuuint64_t>(ld) * 2 * static_cast<cuuint64_t>(seq)};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  cudaFree(nullptr);  // binds the primary context on threads that have not used it yet
+  static thread_local bool context_bound = false;  // once per thread (not allowed during stream capture)
+  if (!context_bound) {
+    cudaFree(nullptr);  // binds the primary context on threads that have not used it yet
+    context_bound = true;
+  }
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

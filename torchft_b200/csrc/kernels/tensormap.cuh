@@ -67,8 +67,13 @@ inline bool make_tensormap(CUtensorMap* out, const void* ptr, int rank, uint32_t
                                       : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   // The encoder is a driver call and needs a current context.  Threads that only ever
   // used the runtime API lazily (autograd worker threads, for one) may not have bound the
-  // primary context yet; a no-op runtime call binds it.
-  cudaFree(nullptr);
+  // primary context yet; a no-op runtime call binds it.  Once per thread: the call is not allowed
+  // while a stream capture is in progress, and after the first time it has nothing left to do.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   CUresult r = fn(out, dt, rank, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
