@@ -98,3 +98,41 @@ def test_engine_trains_and_state_round_trips():
     assert abs(a - b) < 1e-3 * abs(a)
     # the embedding gradient uses atomics, so the two runs agree to rounding, not bit for bit
     torch.testing.assert_close(engine.flat_param.float(), engine2.flat_param.float(), rtol=2e-2, atol=2e-3)
+
+
+def test_forward_backward_is_cuda_graph_capturable():
+    """The kernels make no call that is illegal during stream capture: a whole forward + backward
+    of the model replays from a CUDA graph with the gradients of the eager run."""
+    from torchft_b200.models.llama import Llama, LlamaConfig
+
+    cfg = LlamaConfig.tiny()
+    model = Llama(cfg, device="cuda")
+    model.init_weights(seed=2)
+    gen = torch.Generator().manual_seed(0)
+    tokens = torch.randint(cfg.vocab_size, (2, 128), generator=gen).cuda()
+    targets = torch.randint(cfg.vocab_size, (2, 128), generator=gen).cuda()
+    # everything on a side stream from the start: gradient accumulation nodes created on the
+    # default stream would break the capture (a PyTorch rule, not one of these kernels)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            model.zero_grad(set_to_none=True)
+            loss = model(tokens, targets)
+            loss.backward()
+        eager_loss = float(loss)
+        eager_grads = [p.grad.detach().clone() for p in model.parameters()]
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    model.zero_grad(set_to_none=True)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_loss = model(tokens, targets)
+        static_loss.backward()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert abs(float(static_loss) - eager_loss) < 1e-3
+    for p, ref in zip(model.parameters(), eager_grads):
+        # the embedding gradient is accumulated with atomics: compare with a tolerance
+        torch.testing.assert_close(p.grad.float(), ref.float(), atol=2e-2, rtol=2e-2)
