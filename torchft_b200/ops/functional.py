@@ -84,7 +84,8 @@ _scratch: dict = {}
 
 def _norm_scratch(rows: int, dim: int, device: torch.device) -> torch.Tensor:
     parts = _lib.lib().tft_rmsnorm_bwd_parts(rows)
-    key = (device.index, parts * dim)
+    # one buffer per stream: two streams may run this backward at the same time
+    key = (device.index, parts * dim, _lib.stream_ptr())
     buf = _scratch.get(key)
     if buf is None:
         buf = torch.empty(parts * dim, dtype=torch.float32, device=device)
