@@ -207,3 +207,45 @@ def test_retry_backoff():
     assert not ok and attempts == 3
     ok, attempts = C.retry_backoff_probe(fail_times=10**6, initial_ms=5, timeout_ms=50)
     assert not ok and attempts >= 2
+
+
+# ------------------------------------------------------------------ property checks
+def test_results_invariants_hold_for_random_quorums():
+    """Whatever the steps of the members, the per-replica views of one quorum fit together:
+    ranks are a permutation, recovery sources are up to date, and every replica that is behind is
+    assigned to exactly one source."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=200, deadline=None)
+    @given(steps=st.lists(st.integers(min_value=0, max_value=3), min_size=1, max_size=9), local_rank=st.integers(0, 7))
+    def check(steps, local_rank):
+        members = [member(f"replica_{i:02d}", step=s) for i, s in enumerate(steps)]
+        n = len(members)
+        views = [C.compute_quorum_results(m["replica_id"], local_rank, 1, members) for m in members]
+        max_step = max(steps)
+        cohort = [i for i, s in enumerate(steps) if s == max_step]
+        assert sorted(v.replica_rank for v in views) == list(range(n))
+        primary = cohort[local_rank % len(cohort)]
+        assigned = []
+        for i, v in enumerate(views):
+            assert v.replica_world_size == n and v.max_step == max_step and v.max_world_size == len(cohort)
+            assert v.store_address == members[primary]["store_address"]
+            in_cohort = i in cohort
+            assert (v.max_rank is not None) == in_cohort
+            if in_cohort:
+                assert v.max_rank == cohort.index(i)
+            # at step 0 everybody but the primary takes the primary's weights; later only the stragglers heal
+            expect_heal = (i != primary) if max_step == 0 else not in_cohort
+            assert v.heal == expect_heal, (steps, local_rank, i)
+            if v.heal:
+                assert v.recover_src_rank is not None and v.recover_src_rank in cohort
+                assert v.recover_src_manager_address == members[v.recover_src_rank]["address"]
+                assert v.recover_dst_ranks == []
+            assigned.extend((dst, i) for dst in v.recover_dst_ranks)
+        healing = sorted(i for i, v in enumerate(views) if v.heal)
+        assert sorted(dst for dst, _ in assigned) == healing  # each exactly once
+        for dst, src in assigned:
+            assert views[dst].recover_src_rank == src
+
+    check()
