@@ -249,3 +249,54 @@ def test_results_invariants_hold_for_random_quorums():
             assert views[dst].recover_src_rank == src
 
     check()
+
+
+def test_quorum_compute_invariants_hold_for_random_states():
+    """Safety properties of the lighthouse rule on random states: a quorum is sorted, made of healthy
+    requesters only, at least ``min_replicas`` large, a strict majority of the heartbeating replicas,
+    and never grows when a member of the previous quorum asked to shrink only."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    ids = [f"r{i}" for i in range(6)]
+    replica = st.fixed_dictionaries({
+        "asks": st.booleans(), "beats": st.booleans(), "beat_age": st.floats(0.0, 8.0), "joined_ago": st.floats(0.0, 3.0),
+        "shrink_only": st.booleans(), "in_prev": st.booleans(),
+    })
+
+    @settings(max_examples=300, deadline=None)
+    @given(spec=st.lists(replica, min_size=1, max_size=6), min_replicas=st.integers(1, 4), join_ms=st.sampled_from([0, 1000, 60000]))
+    def check(spec, min_replicas, join_ms):
+        now = 1000.0
+        state = {"participants": {}, "heartbeats": {}, "prev_quorum": None}
+        prev = []
+        for rid, s in zip(ids, spec):
+            if s["beats"]:
+                state["heartbeats"][rid] = now - s["beat_age"]
+            if s["asks"]:
+                state["participants"][rid] = part(rid, now - s["joined_ago"], shrink_only=s["shrink_only"])
+                state["heartbeats"].setdefault(rid, now)  # a request counts as a heartbeat
+            if s["in_prev"]:
+                prev.append(member(rid))
+        if prev:
+            state["prev_quorum"] = {"quorum_id": 1, "participants": prev}
+        members, reason = C.quorum_compute(now, state, min_replicas=min_replicas, join_timeout_ms=join_ms, heartbeat_timeout_ms=5000)
+        assert isinstance(reason, str) and reason
+        if members is None:
+            return
+        got = [m["replica_id"] for m in members]
+        healthy = {rid for rid, t in state["heartbeats"].items() if now - t < 5.0}
+        assert got == sorted(got) and len(set(got)) == len(got)
+        assert set(got) <= set(state["participants"]) & healthy
+        if "Fast quorum" in reason:
+            # every member of the previous quorum is back: accepted at once (with any newcomers), ahead of the
+            # size rules, which that quorum satisfied when it formed
+            assert {m["replica_id"] for m in prev} <= set(got)
+        else:
+            assert len(got) >= min_replicas
+            assert len(got) > len(healthy) / 2  # split-brain guard: a strict majority of the heartbeating replicas
+        shrink = any(state["participants"][rid]["member"]["shrink_only"] for rid in got)
+        if shrink and prev:
+            assert set(got) <= {m["replica_id"] for m in prev}
+
+    check()

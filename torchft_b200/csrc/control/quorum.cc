@@ -57,15 +57,19 @@ std::pair<std::optional<std::vector<wire::QuorumMember>>, std::string> quorum_co
     if (fast) return {candidates, "Fast quorum found! " + metadata};
   }
 
-  if (healthy_participants.size() < opt.min_replicas) {
-    return {std::nullopt, "New quorum not ready, only have " + std::to_string(healthy_participants.size()) +
+  // The size rules are applied to the set that would be returned.  It differs from the healthy
+  // participants only after a shrink_only filter; the reference (src/lighthouse.rs:190-213) counts the
+  // unfiltered set there and can hand out a quorum below min_replicas, a minority, or an empty one.
+  const size_t quorum_size = candidates.size();
+  if (quorum_size < opt.min_replicas) {
+    return {std::nullopt, "New quorum not ready, only have " + std::to_string(quorum_size) +
                               " participants, need min_replicas " + std::to_string(opt.min_replicas) + " " +
                               metadata};
   }
 
   // Split-brain guard: more than half of the replicas known to be alive must take part.
-  if (healthy_participants.size() <= healthy_replicas.size() / 2) {
-    return {std::nullopt, "New quorum not ready, only have " + std::to_string(healthy_participants.size()) +
+  if (quorum_size <= healthy_replicas.size() / 2) {
+    return {std::nullopt, "New quorum not ready, only have " + std::to_string(quorum_size) +
                               " participants, need at least half of " +
                               std::to_string(healthy_replicas.size()) + " healthy workers " + metadata};
   }
