@@ -420,3 +420,39 @@ def test_wire_decoder_rejects_garbage_without_crashing():
             except (RuntimeError, ValueError):
                 outcomes["error"] += 1
     assert outcomes["error"] > 0 and outcomes["ok"] > 0
+
+
+def test_wire_codec_round_trips_random_messages():
+    """Random field values survive this codec -> protobuf runtime -> this codec unchanged."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    QuorumMember, Response = _schema()
+    i64 = st.integers(min_value=-(2**63), max_value=2**63 - 1)
+    text = st.text(max_size=40)
+
+    @settings(max_examples=200, deadline=None)
+    @given(rid=text, addr=text, store=text, step=i64, world=st.integers(0, 2**64 - 1), shrink=st.booleans())
+    def member_round_trip(rid, addr, store, step, world, shrink):
+        d = {"replica_id": rid, "address": addr, "store_address": store, "step": step, "world_size": world, "shrink_only": shrink}
+        theirs = QuorumMember.FromString(C.encode_quorum_member(d))
+        assert (theirs.replica_id, theirs.address, theirs.store_address, theirs.step, theirs.world_size, theirs.shrink_only) == (
+            rid, addr, store, step, world, shrink)
+        assert C.decode_quorum_member(theirs.SerializeToString()) == d
+
+    @settings(max_examples=200, deadline=None)
+    @given(qid=i64, src=text, src_rank=st.none() | i64, dst=st.lists(i64, max_size=6), store=text, max_step=i64,
+           max_rank=st.none() | i64, heal=st.booleans())
+    def response_round_trip(qid, src, src_rank, dst, store, max_step, max_rank, heal):
+        q = C.QuorumResult()
+        q.quorum_id, q.recover_src_manager_address, q.recover_src_rank, q.recover_dst_ranks = qid, src, src_rank, dst
+        q.store_address, q.max_step, q.max_rank, q.heal = store, max_step, max_rank, heal
+        theirs = Response.FromString(C.encode_manager_quorum_response(q))
+        assert theirs.HasField("recover_src_rank") == (src_rank is not None)
+        assert theirs.HasField("max_rank") == (max_rank is not None)
+        back = C.decode_manager_quorum_response(theirs.SerializeToString())
+        assert (back.quorum_id, back.recover_src_manager_address, back.recover_src_rank, back.recover_dst_ranks) == (qid, src, src_rank, dst)
+        assert (back.store_address, back.max_step, back.max_rank, back.heal) == (store, max_step, max_rank, heal)
+
+    member_round_trip()
+    response_round_trip()
