@@ -348,3 +348,40 @@ def test_run_collective_bookkeeping(env):
     assert seen == {}
     manager._client.should_commit.return_value = False
     assert not manager.should_commit()
+
+
+def test_step_accounting_over_random_histories(env):
+    """Whatever mix of failed collectives, refused commits and changing quorum sizes: the step counts
+    committed steps only, batches_committed adds the participants of committed steps, and an error
+    never leaks into the next step."""
+    import random
+
+    manager, pg, _ = env(min_replica_size=1)
+    rng = random.Random(11)
+    step, batches, quorum_id = 0, 0, 100
+    for _ in range(60):
+        if rng.random() < 0.3:
+            quorum_id += 1  # membership changed
+        world = rng.randint(1, 4)
+        manager._client.quorum.return_value = quorum_result(
+            quorum_id=quorum_id, replica_rank=0, replica_world_size=world, max_rank=0, max_world_size=world, max_step=step)
+        fail = rng.random() < 0.25
+        vote = rng.random() < 0.8
+        pg.fail_future = RuntimeError("injected") if fail else None
+        manager._client.should_commit.return_value = vote and not fail
+        manager.start_quorum()
+        assert manager.errored() is None
+        t = torch.ones(3)
+        manager.allreduce(t).wait()
+        committed = manager.should_commit()
+        # the manager votes False after an error whatever the group would answer
+        sent_vote = manager._client.should_commit.call_args.kwargs.get("should_commit", None)
+        if sent_vote is None:
+            sent_vote = manager._client.should_commit.call_args.args[2]
+        assert sent_vote == (not fail)
+        assert committed == (vote and not fail)
+        if committed:
+            step += 1
+            batches += world
+        assert manager.current_step() == step and manager.batches_committed() == batches
+    pg.fail_future = None
