@@ -48,6 +48,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama_1b", "tiny"])
     ap.add_argument("--seq", type=int, default=0, help="sequence length (default: the model's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
+    ap.add_argument("--topology", default="", help="override the layout, '<replica groups>x<shard GPUs>' (default: 1x1, 2x1, 2x2, 2x4)")
     ap.add_argument("--fused-gather", action="store_true",
                     help="shard every projection matrix by rows and gather it inside its first GEMM of the step "
                          "(all-gather fused GEMM) instead of with separate all-gather kernels")
@@ -142,6 +143,11 @@ def run_ours(args: argparse.Namespace) -> None:
     if args.gpus not in TOPOLOGY:
         raise SystemExit(f"--gpus must be one of {sorted(TOPOLOGY)}")
     n_groups, shard_world = TOPOLOGY[args.gpus]
+    if args.topology:
+        # experiments only: "<replica groups>x<shard GPUs>", e.g. 1x2 to study sharding without replication
+        n_groups, shard_world = (int(v) for v in args.topology.lower().split("x"))
+        if n_groups * shard_world != args.gpus:
+            raise SystemExit(f"--topology {args.topology} does not multiply to --gpus {args.gpus}")
     group, shard_rank = divmod(rank, shard_world)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
