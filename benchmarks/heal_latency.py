@@ -2,6 +2,7 @@
 
     python benchmarks/heal_latency.py --transport nvlink --model llama_1b --steps 600 --kill-at 40
     python benchmarks/heal_latency.py --transport http   --model llama_1b --steps 600 --kill-at 40
+    python benchmarks/heal_latency.py --transport nvlink --model llama_1b --steps 1000 --kill-at 200 --kills 4
 
 Two replica groups of one GPU each train a Llama-shape model under per-step quorum.  After
 ``--kill-at`` committed steps replica 1 leaves (its process exits between two steps, with
@@ -12,6 +13,9 @@ the quorum, pulls parameters and AdamW state from the survivor and resumes.  Rep
   ``heal_bytes`` and the resulting GB/s;
 * ``rejoin_s``: from the newcomer's ``Manager`` being up to its first committed step;
 * on the survivor: steps that did not commit and the median step time before / after.
+
+With ``--kills N`` the replica leaves N times, every ``--kill-at`` steps, and each newcomer heals from
+the survivor; the summary then carries the median and the worst heal and rejoin times.
 
 ``--transport http`` uses the serialising HTTP transport (the reference's method,
 ``torchft/checkpointing.py``), ``nvlink`` the peer-memory transport.  The failure is injected
@@ -97,10 +101,13 @@ def worker(args: argparse.Namespace) -> None:
             first_commit_s = time.perf_counter() - t_up
         if not committed:
             uncommitted += 1
-        if args.rank == 1 and not args.restarted and manager.current_step() >= args.kill_at:
+        if args.rank == 1 and args.kill_at > 0 and manager.current_step() >= args.kill_at:
             # leave between steps: nothing of ours is in flight on the GPU
             torch.cuda.synchronize()
-            print(json.dumps({"event": "replica_left", "step": manager.current_step()}), flush=True)
+            heal = tracing.summary().get("tft.heal_recv", {"calls": 0, "total_s": 0.0})
+            print(json.dumps({"event": "replica_left", "step": manager.current_step(), "restarted": args.restarted,
+                              "heal_calls": heal["calls"], "heal_s": round(heal["total_s"], 4),
+                              "rejoin_s": round(first_commit_s, 3) if first_commit_s is not None else None}), flush=True)
             os._exit(0)
     torch.cuda.synchronize()
     heal = tracing.summary().get("tft.heal_recv", {"calls": 0, "total_s": 0.0})
@@ -131,28 +138,47 @@ def parent(args: argparse.Namespace) -> None:
     base = [sys.executable, os.path.abspath(__file__), "--worker", "--lighthouse", lighthouse.address(), "--transport",
             args.transport, "--model", args.model, "--steps", str(args.steps), "--kill-at", str(args.kill_at),
             "--timeout", str(args.timeout), "--device-timeout", str(args.device_timeout)]
-    procs = {r: subprocess.Popen(base + ["--rank", str(r)], stdout=subprocess.PIPE, text=True) for r in (0, 1)}
-    out1, _ = procs[1].communicate(timeout=1800)
-    t_left = time.perf_counter()
-    print(out1.strip().splitlines()[-1] if out1.strip() else "{}")
-    # a supervisor (torchrun, a scheduler) would restart the group; do the same
-    procs[1] = subprocess.Popen(base + ["--rank", "1", "--restarted"], stdout=subprocess.PIPE, text=True)
+
+    def start(rank: int, kill_at: int, restarted: bool) -> subprocess.Popen:
+        cmd = [a for a in base]
+        cmd[cmd.index("--kill-at") + 1] = str(kill_at)
+        cmd += ["--rank", str(rank)] + (["--restarted"] if restarted else [])
+        return subprocess.Popen(cmd, stdout=subprocess.PIPE, text=True)
+
     results = []
-    for r in (1, 0):
-        out, _ = procs[r].communicate(timeout=3600)
+
+    def collect(out: str) -> None:
         for line in out.strip().splitlines():
             if line.startswith("{"):
                 results.append(json.loads(line))
                 print(line)
+
+    survivor = start(0, 0, False)
+    replica = start(1, args.kill_at, False)
+    for k in range(args.kills):
+        out, _ = replica.communicate(timeout=1800)
+        collect(out)
+        # a supervisor (torchrun, a scheduler) would restart the group; do the same
+        next_kill = args.kill_at * (k + 2) if k + 1 < args.kills else 0
+        replica = start(1, next_kill, True)
+    for proc in (replica, survivor):
+        out, _ = proc.communicate(timeout=3600)
+        collect(out)
     lighthouse.shutdown()
-    newcomer = next((x for x in results if x.get("restarted")), None)
-    survivor = next((x for x in results if x.get("rank") == 0), None)
-    if newcomer and survivor:
+    heals = [x for x in results if x.get("restarted") and x.get("heal_calls")]
+    survivor_result = next((x for x in results if x.get("event") == "result" and x.get("rank") == 0), None)
+    last = next((x for x in results if x.get("event") == "result" and x.get("restarted")), None)
+    if heals and survivor_result:
+        heal_s = [x["heal_s"] for x in heals]
+        rejoin_s = [x["rejoin_s"] for x in heals if x.get("rejoin_s") is not None]
         print(json.dumps({
-            "summary": "heal", "transport": args.transport, "model": args.model,
-            "heal_s": newcomer["heal_s"], "heal_GBps": newcomer["heal_GBps"], "heal_bytes": newcomer["heal_bytes"],
-            "rejoin_s": newcomer["rejoin_s"], "survivor_uncommitted_steps": survivor["uncommitted_steps"],
-            "tokens_per_s_two_replicas": survivor["tokens_per_s_two_replicas"],
+            "summary": "heal", "transport": args.transport, "model": args.model, "kills": args.kills,
+            "heal_s": round(statistics.median(heal_s), 4), "heal_s_max": max(heal_s),
+            "heal_GBps": last["heal_GBps"] if last else None, "heal_bytes": last["heal_bytes"] if last else None,
+            "rejoin_s": round(statistics.median(rejoin_s), 3) if rejoin_s else None,
+            "rejoin_s_max": max(rejoin_s) if rejoin_s else None,
+            "survivor_uncommitted_steps": survivor_result["uncommitted_steps"],
+            "tokens_per_s_two_replicas": survivor_result["tokens_per_s_two_replicas"],
         }))
 
 
@@ -165,7 +191,8 @@ def main() -> None:
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "http"])
     ap.add_argument("--model", default="llama_1b", choices=["llama3_8b", "llama_1b", "tiny"])
     ap.add_argument("--steps", type=int, default=600)
-    ap.add_argument("--kill-at", type=int, default=40)
+    ap.add_argument("--kill-at", type=int, default=40, help="replica 1 leaves after this many committed steps (0: never)")
+    ap.add_argument("--kills", type=int, default=1, help="how many times the replica leaves (every --kill-at steps)")
     ap.add_argument("--timeout", type=float, default=300.0)
     ap.add_argument("--device-timeout", type=float, default=30.0)
     ap.add_argument("--join-timeout-ms", type=int, default=200)
