@@ -338,32 +338,54 @@ diloco_outer_kernel(Comm c, OuterArgs a) {
   const float4* min4 = reinterpret_cast<const float4*>(a.mom_in);
   float4* mout4 = reinterpret_cast<float4*>(a.mom_out);
   uint4* gout = static_cast<uint4*>(a.global_out);
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < a.nvec; i += stride) {
-    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    Vec<T>::add(g, ld_peer_v4(c.heap[c.rank] + a.off_g + i * 16));
-    Vec<T>::add(w, gin[i]);
-    float b[8];
-    if (a.mu != 0.f) {
+  // two vectors per thread and round: all loads of both are issued before the arithmetic
+  constexpr int UNR2 = 2;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < a.nvec; i0 += stride * UNR2) {
+    uint4 gv[UNR2], wv[UNR2];
+    float4 mv[UNR2][N / 4];
 #pragma unroll
-      for (int q = 0; q < N / 4; ++q) {
-        float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!a.first) m = min4[i * (N / 4) + q];
-        b[4 * q] = m.x; b[4 * q + 1] = m.y; b[4 * q + 2] = m.z; b[4 * q + 3] = m.w;
+    for (int u = 0; u < UNR2; ++u) {
+      const long long i = i0 + u * stride;
+      gv[u] = wv[u] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int q = 0; q < N / 4; ++q) mv[u][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < a.nvec) {
+        gv[u] = ld_peer_v4(c.heap[c.rank] + a.off_g + i * 16);
+        wv[u] = gin[i];
+        if (a.mu != 0.f && !a.first) {
+#pragma unroll
+          for (int q = 0; q < N / 4; ++q) mv[u][q] = min4[i * (N / 4) + q];
+        }
       }
-#pragma unroll
-      for (int j = 0; j < N; ++j) {
-        b[j] = a.first ? g[j] : a.mu * b[j] + g[j];
-        const float step = a.nesterov ? g[j] + a.mu * b[j] : b[j];
-        w[j] -= a.lr * step;
-      }
-#pragma unroll
-      for (int q = 0; q < N / 4; ++q)
-        mout4[i * (N / 4) + q] = make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < N; ++j) w[j] -= a.lr * g[j];
     }
-    gout[i] = Vec<T>::pack(w, 1.f);
+#pragma unroll
+    for (int u = 0; u < UNR2; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= a.nvec) break;
+      float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      Vec<T>::add(g, gv[u]);
+      Vec<T>::add(w, wv[u]);
+      if (a.mu != 0.f) {
+        float b[8];
+#pragma unroll
+        for (int q = 0; q < N / 4; ++q) {
+          b[4 * q] = mv[u][q].x; b[4 * q + 1] = mv[u][q].y; b[4 * q + 2] = mv[u][q].z; b[4 * q + 3] = mv[u][q].w;
+        }
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          b[j] = a.first ? g[j] : a.mu * b[j] + g[j];
+          const float step = a.nesterov ? g[j] + a.mu * b[j] : b[j];
+          w[j] -= a.lr * step;
+        }
+#pragma unroll
+        for (int q = 0; q < N / 4; ++q)
+          mout4[i * (N / 4) + q] = make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) w[j] -= a.lr * g[j];
+      }
+      gout[i] = Vec<T>::pack(w, 1.f);
+    }
   }
 }
 
