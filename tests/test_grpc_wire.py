@@ -466,3 +466,33 @@ def test_server_survives_garbage_frames():
             _unary(ch, "/torchft.LighthouseService/Heartbeat", S.LighthouseHeartbeatRequest(replica_id="after"), S.Empty)
     finally:
         lighthouse.shutdown()
+
+
+def test_hpack_decoder_on_random_blocks():
+    """Random header blocks decode to a list or to None; re-encoding what decoded gives the same headers."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=300, deadline=None)
+    @given(block=st.binary(max_size=96))
+    def check(block):
+        out = C.HpackDecoder().decode(block)
+        if out is None:
+            return
+        headers = [(k.decode("latin-1"), v.decode("latin-1")) for k, v in out]
+        if any(ord(ch) > 255 for k, v in headers for ch in k + v):
+            return
+        # latin-1 text survives the Python <-> C++ string conversion only for ASCII; keep to that
+        if not all(k.isascii() and v.isascii() for k, v in headers):
+            return
+        again = C.HpackDecoder().decode(C.hpack_encode(headers, True))
+        assert again == out
+
+    check()
+
+    @settings(max_examples=200, deadline=None)
+    @given(data=st.binary(max_size=64))
+    def huffman(data):
+        assert C.huffman_decode(C.huffman_encode(data)) == data
+
+    huffman()
