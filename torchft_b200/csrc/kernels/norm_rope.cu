@@ -153,15 +153,25 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
   }
 }
 
-// dw[c] (+)= sum_p partial[p, c]
+// dw[c] (+)= sum_p partial[p, c].  A block of 256 threads covers 32 columns with 8 slices of the
+// partial rows each (a warp reads 128 contiguous bytes per row), so dim / 32 blocks share the work.
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw,
                                          int parts, int dim, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
+  __shared__ float acc[8][33];
+  const int col = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + col;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[static_cast<size_t>(p) * dim + c];
-  if (accumulate) s += __bfloat162float(dw[c]);
-  dw[c] = __float2bfloat16(s);
+  if (c < dim)
+    for (int p = slice; p < parts; p += 8) s += partial[static_cast<size_t>(p) * dim + c];
+  acc[slice][col] = s;
+  __syncthreads();
+  if (slice == 0 && c < dim) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += acc[k][col];
+    if (accumulate) t += __bfloat162float(dw[c]);
+    dw[c] = __float2bfloat16(t);
+  }
 }
 
 // Rotary embedding in place on x[tokens, heads, hd], pairing element i with i + hd/2.
@@ -263,7 +273,7 @@ TFT_API int tft_rmsnorm_bwd(const void* dy, const void* x, const void* w, const 
     case 3: rmsnorm_bwd_kernel<3><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
     default: rmsnorm_bwd_kernel<4><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
   }
-  rmsnorm_dw_reduce_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(scratch, static_cast<__nv_bfloat16*>(dw), parts,
+  rmsnorm_dw_reduce_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(scratch, static_cast<__nv_bfloat16*>(dw), parts,
                                                                   dim, accumulate);
   return static_cast<int>(cudaGetLastError());
 }
@@ -372,7 +382,7 @@ TFT_API int tft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w
     case 3: rmsnorm_bwd_kernel<3><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
     default: rmsnorm_bwd_kernel<4><<<parts, threads, 0, stream>>>(DY, X, W, rstd, DR, DX, scratch, rows, dim); break;
   }
-  rmsnorm_dw_reduce_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(scratch, static_cast<__nv_bfloat16*>(dw), parts,
+  rmsnorm_dw_reduce_kernel<<<(dim + 31) / 32, 256, 0, stream>>>(scratch, static_cast<__nv_bfloat16*>(dw), parts,
                                                                   dim, accumulate);
   return static_cast<int>(cudaGetLastError());
 }
