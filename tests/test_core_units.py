@@ -4,6 +4,7 @@ Scenarios follow the reference's futures_test.py, checkpointing_test.py, optim_t
 data_test.py and ddp_test.py.
 """
 
+import os
 import threading
 import time
 import urllib.error
@@ -206,3 +207,32 @@ def test_pure_ddp_hooks_every_parameter():
     ddp = PureDistributedDataParallel(manager, m)
     ddp(torch.rand(2, 3)).mean().backward()
     assert sorted(calls) == sorted(p.numel() for p in m.parameters())
+
+
+# ------------------------------------------------------------------ durable checkpoints
+def test_durable_checkpoint_round_trip(tmp_path):
+    from unittest.mock import MagicMock
+
+    from torchft_b200.utils.durable import latest_step, load_checkpoint, save_checkpoint
+
+    manager = MagicMock()
+    manager.current_step.return_value = 7
+    manager.state_dict.return_value = {"step": 7, "batches_committed": 14}
+    model = nn.Linear(3, 2)
+    for rank in (0, 1):
+        path = save_checkpoint(str(tmp_path), manager, {"model": model.state_dict(), "rank": rank}, rank=rank,
+                               dataloader_state={"position": 70})
+        assert path.endswith(f"step0000000007/rank{rank:05d}.pt")
+    # a newer step that only rank 0 finished writing does not count for a two-rank job
+    manager.current_step.return_value = 9
+    manager.state_dict.return_value = {"step": 9, "batches_committed": 18}
+    save_checkpoint(str(tmp_path), manager, {"model": model.state_dict(), "rank": 0}, rank=0)
+    assert latest_step(str(tmp_path), world_size=2) == 7 and latest_step(str(tmp_path), world_size=1) == 9
+    assert not [f for f in os.listdir(tmp_path / "step0000000007") if f.startswith(".tmp-")]
+
+    restored = MagicMock()
+    out = load_checkpoint(str(tmp_path), restored, rank=1, world_size=2)
+    restored.load_state_dict.assert_called_once_with({"step": 7, "batches_committed": 14})
+    assert out["user"]["rank"] == 1 and out["dataloader"] == {"position": 70}
+    assert torch.equal(out["user"]["model"]["weight"], model.state_dict()["weight"])
+    assert load_checkpoint(str(tmp_path / "nothing"), restored) is None
