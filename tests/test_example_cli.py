@@ -18,9 +18,10 @@ def _free_port():
     return p
 
 
-def test_train_ddp_example_two_replica_groups():
+def test_train_ddp_example_two_replica_groups(tmp_path):
     lh_port = _free_port()
-    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", TORCHFT_B200_LOG="")
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", TORCHFT_B200_LOG="", CHECKPOINT_DIR=str(tmp_path),
+               CHECKPOINT_EVERY="2")
     lighthouse = subprocess.Popen(
         [sys.executable, "-m", "torchft_b200.lighthouse", "--min_replicas", "2", "--bind", f"[::]:{lh_port}",
          "--join_timeout_ms", "20000"],
@@ -50,6 +51,10 @@ def test_train_ddp_example_two_replica_groups():
             assert w.returncode == 0, out.decode()[-3000:]
         status = urllib.request.urlopen(f"http://127.0.0.1:{lh_port}/status", timeout=5).read().decode()
         assert "train_ddp_0" in status and "train_ddp_1" in status
+        # replica group 0 left durable checkpoints behind (manager state included)
+        from torchft_b200.utils.durable import latest_step
+
+        assert latest_step(str(tmp_path)) is not None and latest_step(str(tmp_path)) >= 2
     finally:
         for w in workers:
             if w.poll() is None:

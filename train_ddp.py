@@ -94,8 +94,19 @@ def main() -> None:
     criterion = nn.CrossEntropyLoss()
     print(model)
 
-    # A durable checkpoint must contain, besides model and optimizer:
-    #   manager.state_dict()  (step and batches_committed)  and the dataloader position.
+    # Durable checkpoints (optional): besides model and optimizer they hold manager.state_dict()
+    # (step and batches_committed).  One replica group writes; every group reads after a full restart.
+    ckpt_dir = os.environ.get("CHECKPOINT_DIR")
+    ckpt_every = int(os.environ.get("CHECKPOINT_EVERY", 100))
+    if ckpt_dir:
+        from torchft_b200.utils.durable import load_checkpoint, save_checkpoint
+
+        restored = load_checkpoint(ckpt_dir, manager, rank=int(os.environ.get("RANK", 0)),
+                                   world_size=int(os.environ.get("WORLD_SIZE", 1)))
+        if restored is not None:
+            load_state_dict(restored["user"])
+            print(f"resumed from step {manager.current_step()}")
+    last_saved = manager.current_step()
     while True:
         for inputs, labels in loader:
             inputs, labels = inputs.to(device), labels.to(device)
@@ -105,6 +116,9 @@ def main() -> None:
             optimizer.step()  # applied only if every rank of the group voted to commit
             if manager.current_step() % 100 == 0:
                 print(f"[{manager.current_step()}] loss = {loss.item():.4f} participants = {manager.num_participants()}")
+            if ckpt_dir and replica_group == 0 and manager.current_step() >= last_saved + ckpt_every:
+                save_checkpoint(ckpt_dir, manager, state_dict(), rank=int(os.environ.get("RANK", 0)))
+                last_saved = manager.current_step()
             if manager.current_step() >= total_steps:
                 manager.shutdown(wait=False)
                 sys.exit(0)
