@@ -3,28 +3,39 @@
 Public API (same names as ``torchft``): ``Manager``, ``Optimizer``,
 ``DistributedDataParallel``, ``DistributedSampler``, ``ProcessGroupGloo``,
 ``ProcessGroupBabyNCCL`` plus the B200-native ``ProcessGroupNVLink``.
+
+Names are resolved on first use, so that ``torchft_b200.utils.build`` can be imported (and the
+native parts built) in a fresh checkout where the compiled control plane does not exist yet.
 """
 
-from torchft_b200.data import DistributedSampler
-from torchft_b200.ddp import DistributedDataParallel
-from torchft_b200.manager import Manager
-from torchft_b200.optim import OptimizerWrapper as Optimizer
-from torchft_b200.process_group import ProcessGroupBabyNCCL, ProcessGroupGloo
+import importlib
 
-__all__ = (
-    "DistributedDataParallel",
-    "DistributedSampler",
-    "Manager",
-    "Optimizer",
-    "ProcessGroupBabyNCCL",
-    "ProcessGroupGloo",
-)
+_EXPORTS = {
+    "DistributedSampler": ("torchft_b200.data", "DistributedSampler"),
+    "DistributedDataParallel": ("torchft_b200.ddp", "DistributedDataParallel"),
+    "Manager": ("torchft_b200.manager", "Manager"),
+    "Optimizer": ("torchft_b200.optim", "OptimizerWrapper"),
+    "ProcessGroupBabyNCCL": ("torchft_b200.process_group", "ProcessGroupBabyNCCL"),
+    "ProcessGroupGloo": ("torchft_b200.process_group", "ProcessGroupGloo"),
+    # the NVLink backend pulls in the CUDA kernel library
+    "ProcessGroupNVLink": ("torchft_b200.parallel.nvlink", "ProcessGroupNVLink"),
+}
+
+__all__ = tuple(sorted(k for k in _EXPORTS if k != "ProcessGroupNVLink"))
 
 
 def __getattr__(name: str):
-    # resolved on first use: the NVLink backend pulls in the CUDA kernel library
-    if name == "ProcessGroupNVLink":
-        from torchft_b200.parallel.nvlink import ProcessGroupNVLink
+    target = _EXPORTS.get(name)
+    if target is None:
+        # submodules (torchft_b200._control, torchft_b200.manager, ...) still import the usual way
+        try:
+            return importlib.import_module(f"{__name__}.{name}")
+        except ModuleNotFoundError:
+            raise AttributeError(f"module 'torchft_b200' has no attribute {name!r}") from None
+    value = getattr(importlib.import_module(target[0]), target[1])
+    globals()[name] = value
+    return value
 
-        return ProcessGroupNVLink
-    raise AttributeError(f"module 'torchft_b200' has no attribute {name!r}")
+
+def __dir__():
+    return sorted(list(globals()) + list(_EXPORTS))
