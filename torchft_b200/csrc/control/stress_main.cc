@@ -19,6 +19,7 @@
 #include <thread>
 #include <vector>
 
+#include "h2.h"
 #include "lighthouse.h"
 #include "manager.h"
 
@@ -100,6 +101,47 @@ void garbage_client(int port, unsigned seed) {
   ::close(fd);
 }
 
+// Feeds random and truncated buffers to every protobuf decoder and to the HPACK decoder; under
+// AddressSanitizer an out-of-bounds read in a parser shows up here.
+void fuzz_decoders() {
+  unsigned state = 12345;
+  auto next = [&state] {
+    state = state * 1664525u + 1013904223u;
+    return state >> 8;
+  };
+  wire::QuorumMember m;
+  m.replica_id = "replica";
+  m.address = "http://host:1";
+  m.store_address = "host:2";
+  m.step = 7;
+  m.world_size = 3;
+  wire::Quorum q;
+  q.quorum_id = 5;
+  q.participants = {m, m};
+  const std::string good = q.encode();
+  for (int i = 0; i < 20000; ++i) {
+    std::string buf;
+    if (i % 3 == 0) {
+      buf = good.substr(0, next() % (good.size() + 1));
+      if (!buf.empty()) buf[next() % buf.size()] = static_cast<char>(next() & 0xff);
+    } else {
+      const unsigned len = next() % 48;
+      for (unsigned j = 0; j < len; ++j) buf.push_back(static_cast<char>(next() & 0xff));
+    }
+    try { wire::QuorumMember::decode(buf); } catch (const std::exception&) {}
+    try { wire::Quorum::decode(buf); } catch (const std::exception&) {}
+    try { wire::LighthouseQuorumRequest::decode(buf); } catch (const std::exception&) {}
+    try { wire::ManagerQuorumRequest::decode(buf); } catch (const std::exception&) {}
+    try { wire::ManagerQuorumResponse::decode(buf); } catch (const std::exception&) {}
+    try { wire::ShouldCommitRequest::decode(buf); } catch (const std::exception&) {}
+    try { wire::KillRequest::decode(buf); } catch (const std::exception&) {}
+    std::vector<net::h2::Header> headers;
+    net::h2::HpackDecoder().decode(buf, &headers);
+    std::string text;
+    net::h2::huffman_decode(reinterpret_cast<const uint8_t*>(buf.data()), buf.size(), &text);
+  }
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -107,6 +149,7 @@ int main(int argc, char** argv) {
   const int ranks = argc > 2 ? std::atoi(argv[2]) : 2;
   const int rounds = argc > 3 ? std::atoi(argv[3]) : 24;
   net::set_log_enabled(false);
+  fuzz_decoders();
   if (argc > 4) net::set_rpc_protocol(argv[4]);  // "framed" or "grpc": wire protocol of every client in here
 
   LighthouseOptions opt;
