@@ -1,9 +1,10 @@
 """Race and memory-error detection for the C++ control plane.
 
 The lighthouse, the manager servers and their clients are compiled together with a native
-stress harness (``csrc/control/stress_main.cc``) under ThreadSanitizer and under
-AddressSanitizer and run in one process: quorum and should_commit rounds from many threads,
-dashboard polling, and a replica group that goes away half way through.
+stress harness (``csrc/control/stress_main.cc``) under ThreadSanitizer, AddressSanitizer and
+UndefinedBehaviorSanitizer and run in one process: decoder fuzzing, quorum and should_commit rounds
+from many threads, dashboard polling, garbage HTTP/2 clients, and a replica group that goes away
+half way through.
 """
 
 import os
@@ -24,7 +25,8 @@ def _compiler():
     return cxx
 
 
-@pytest.mark.parametrize("sanitizer,marker", [("thread", "ThreadSanitizer"), ("address", "AddressSanitizer")])
+@pytest.mark.parametrize("sanitizer,marker", [("thread", "ThreadSanitizer"), ("address", "AddressSanitizer"),
+                                              ("undefined", "runtime error:")])
 def test_control_plane_under_sanitizer(tmp_path, sanitizer, marker):
     cxx = _compiler()
     exe = tmp_path / f"stress_{sanitizer}"
