@@ -496,3 +496,19 @@ def test_hpack_decoder_on_random_blocks():
         assert C.huffman_decode(C.huffman_encode(data)) == data
 
     huffman()
+
+
+def test_compressed_request_is_refused_with_unimplemented():
+    S = _schema()
+    lighthouse = C.Lighthouse(bind="[::]:0", min_replicas=1, join_timeout_ms=100, quorum_tick_ms=10)
+    try:
+        port = lighthouse.address().rsplit(":", 1)[1]
+        with grpc.insecure_channel(f"127.0.0.1:{port}", compression=grpc.Compression.Gzip) as ch:
+            with pytest.raises(grpc.RpcError) as err:
+                # long enough for the client to bother compressing
+                _unary(ch, "/torchft.LighthouseService/Heartbeat", S.LighthouseHeartbeatRequest(replica_id="z" * 4096), S.Empty)
+            assert err.value.code() == grpc.StatusCode.UNIMPLEMENTED
+        with grpc.insecure_channel(f"127.0.0.1:{port}") as ch:
+            _unary(ch, "/torchft.LighthouseService/Heartbeat", S.LighthouseHeartbeatRequest(replica_id="plain"), S.Empty)
+    finally:
+        lighthouse.shutdown()

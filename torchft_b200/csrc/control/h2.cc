@@ -655,8 +655,10 @@ void serve_connection(int fd, const std::string& prefix, const std::atomic<bool>
         st = Status::Error(kInvalidArgument, "not a gRPC request");
       } else if (tmo != nullptr && !ctx.timeout) {
         st = Status::Error(kInvalidArgument, "invalid timeout " + *tmo);
+      } else if (!data.empty() && data[0] == '\1') {
+        st = Status::Error(12 /*Unimplemented*/, "message compression is not supported (send grpc-encoding: identity)");
       } else if (!grpc_unframe(data, &message)) {
-        st = Status::Error(kInternal, "malformed or compressed gRPC message");
+        st = Status::Error(kInternal, "malformed gRPC message");
       } else {
         try {
           st = dispatch(*path, ctx, message, &resp);
