@@ -68,7 +68,7 @@ def test_lighthouse_quorum_id_stable_until_membership_changes():
             time.sleep(0.02)
             fb = ex.submit(b.quorum, requester("b", step=0), 5 * SEC)
             qa, qb = fa.result(), fb.result()
-        # a alone may have been served by a fast quorum before b arrived; then b joins next round
+        # a alone may have been served by a fast quorum before b arrived; then b joins the next quorum
         ids = {p["replica_id"] for p in qb["participants"]}
         assert "b" in ids
         assert qb["quorum_id"] > q1["quorum_id"]
@@ -101,7 +101,7 @@ def test_lighthouse_join_during_shrink():
             assert [p["replica_id"] for p in q0["participants"]] == ["replica0", "replica1"]
             assert q0["quorum_id"] == first_id  # same members, same id
             assert not f2.done()  # still waiting
-            # 3. next round without shrink_only admits replica2
+            # 3. the next quorum without shrink_only admits replica2
             f0 = ex.submit(c[0].quorum, requester("replica0", 3), 5 * SEC)
             f1 = ex.submit(c[1].quorum, requester("replica1", 3), 5 * SEC)
             q2 = f2.result()
