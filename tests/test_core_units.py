@@ -60,7 +60,7 @@ def test_future_timeout_passes_result_and_exception():
 
 def test_future_timeout_many_deadlines_in_order():
     futs = [Future() for _ in range(20)]
-    timed = [future_timeout(f, timedelta(seconds=0.02 + 0.001 * i)) for i, f in enumerate(futs)]
+    timed = [future_timeout(f, timedelta(seconds=0.3 + 0.001 * i)) for i, f in enumerate(futs)]
     futs[3].set_result("ok")
     assert timed[3].wait() == "ok"
     for i, t in enumerate(timed):

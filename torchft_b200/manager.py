@@ -19,16 +19,21 @@ Behaviour and public API follow the reference's ``torchft/manager.py:73-680``.  
 averaging itself is delegated to ``ProcessGroup.allreduce_scaled`` so a backend with a
 fused kernel (NVLink) does sum, 1/n scaling and the zero contribution of a healing
 replica in one pass instead of three.
+
+Internally the class is cut into four pieces: the *view* of the current quorum (who takes
+part, at which rank), the *ledger* of committed steps, one *round* of quorum work that runs on
+a worker thread (request, reconfiguration, serving and fetching recovery state), and the
+*vote* at the end of the step.
 """
 
 from __future__ import annotations
 
-import concurrent.futures
 import logging
 import os
 import socket
 import uuid
-from concurrent.futures import ThreadPoolExecutor
+from concurrent.futures import Future as _ThreadFuture, ThreadPoolExecutor
+from dataclasses import dataclass
 from datetime import timedelta
 from enum import Enum
 from typing import TYPE_CHECKING, Callable, Dict, List, Optional, TypeVar, cast
@@ -44,9 +49,11 @@ from torchft_b200.utils.tracing import trace_range
 if TYPE_CHECKING:
     from torchft_b200.process_group import ProcessGroup
 
+# keys of the replica group's store through which rank 0 publishes its manager server
 MANAGER_ADDR_KEY: str = "manager_addr"
-MANAGER_PORT_ENV: str = "TORCHFT_MANAGER_PORT"
 REPLICA_ID_KEY: str = "replica_id"
+# environment variable with the port of the manager server (rank 0; default: any free port)
+MANAGER_PORT_ENV: str = "TORCHFT_MANAGER_PORT"
 
 T = TypeVar("T")
 
@@ -61,6 +68,42 @@ class WorldSizeMode(Enum):
 
     DYNAMIC = 0
     FIXED_WITH_SPARES = 1
+
+
+@dataclass
+class _QuorumView:
+    """What the last quorum means for this replica."""
+
+    replica_rank: int = 0             # position among ALL members (recovering ones included)
+    replica_world: int = 0
+    active_rank: Optional[int] = None  # position among the members whose data counts; None = spare / behind
+    active_world: int = 0
+
+
+@dataclass
+class _Ledger:
+    step: int = 0     # committed steps = version of the weights
+    batches: int = 0  # sum over committed steps of the replicas that took part
+
+    def commit(self, participants: int) -> None:
+        self.step += 1
+        self.batches += participants
+
+    def as_dict(self) -> Dict[str, int]:
+        return {"step": self.step, "batches_committed": self.batches}
+
+
+def _from_env(value, name: str, convert=str, zero_is_value: bool = False):
+    """``value`` if given, else the environment variable ``name`` (KeyError when missing).
+    Empty strings and, unless ``zero_is_value``, zeros count as "not given"."""
+    given = value is not None and (zero_is_value or bool(value))
+    return value if given else convert(os.environ[name])
+
+
+def _done(value: T) -> "torch.futures.Future[T]":
+    fut: torch.futures.Future = torch.futures.Future()
+    fut.set_result(value)
+    return fut
 
 
 class Manager:
@@ -109,78 +152,71 @@ class Manager:
             hostname: rank 0 only, the name advertised to the lighthouse
             checkpoint_transport: how recovering replicas fetch state (default HTTP)
         """
-        self._load_state_dict = load_state_dict
-        self._user_state_dict = state_dict
-        self._pending_state_dict: Optional[Dict[str, object]] = None
-        self._use_async_quorum = use_async_quorum
-        self._timeout = timeout
-        self._quorum_timeout = quorum_timeout
-        self._connect_timeout = connect_timeout
-        self._world_size_mode = world_size_mode
-        self._min_replica_size = min_replica_size
-
-        store_addr = store_addr or os.environ["MASTER_ADDR"]
-        store_port = store_port or int(os.environ["MASTER_PORT"])
-        self._rank: int = rank if rank is not None else int(os.environ["RANK"])
-        rank = self._rank
-        world_size = world_size or int(os.environ["WORLD_SIZE"])
-
-        if checkpoint_transport is None:
-            checkpoint_transport = CheckpointServer[Dict[str, T]](timeout=timeout)
-        self._checkpoint_transport: CheckpointTransport[Dict[str, T]] = checkpoint_transport
-
-        self._executor = ThreadPoolExecutor(max_workers=1, thread_name_prefix="async_quorum")
-        self._quorum_future: Optional[concurrent.futures.Future] = None
-
-        self._store = TCPStore(host_name=store_addr, port=store_port, is_master=False, wait_for_workers=False)
+        # ---- configuration
         self._pg = pg
+        self._use_async_quorum = use_async_quorum
+        self._timeout, self._quorum_timeout, self._connect_timeout = timeout, quorum_timeout, connect_timeout
+        self._min_replica_size = min_replica_size
+        self._world_size_mode = world_size_mode
+        self._load_state_dict, self._user_state_dict = load_state_dict, state_dict
+        self._checkpoint_transport: CheckpointTransport[Dict[str, T]] = (
+            checkpoint_transport if checkpoint_transport is not None else CheckpointServer[Dict[str, T]](timeout=timeout)
+        )
+
+        # ---- place in the replica group and its store
+        self._rank: int = int(_from_env(rank, "RANK", int, zero_is_value=True))
+        group_size = int(_from_env(world_size, "WORLD_SIZE", int))
+        host = _from_env(store_addr, "MASTER_ADDR")
+        store_port = int(_from_env(store_port, "MASTER_PORT", int))
+        self._store = TCPStore(host_name=host, port=store_port, is_master=False, wait_for_workers=False)
+
+        # ---- control plane: rank 0 hosts the group's manager server, every rank is its client
         self._manager: Optional[_ManagerServer] = None
-
-        if rank == 0:
-            if port is None:
-                port = int(os.environ.get(MANAGER_PORT_ENV, 0))
-            lighthouse_addr = lighthouse_addr or os.environ["TORCHFT_LIGHTHOUSE"]
-            replica_id = (replica_id or "") + str(uuid.uuid4())
-            self._manager = _ManagerServer(
-                replica_id=replica_id,
-                lighthouse_addr=lighthouse_addr,
-                hostname=hostname,
-                bind=f"[::]:{port}",
-                store_addr=f"{store_addr}:{store_port}",
-                world_size=world_size,
-                heartbeat_interval=heartbeat_interval,
-                connect_timeout=connect_timeout,
+        if self._rank == 0:
+            self._manager = self._host_group_server(
+                replica_id, lighthouse_addr, hostname, port, f"{host}:{store_port}", group_size, heartbeat_interval
             )
-            self._store.set(MANAGER_ADDR_KEY, self._manager.address())
-            self._store.set(REPLICA_ID_KEY, replica_id)
+        self._client = ManagerClient(self._store.get(MANAGER_ADDR_KEY).decode("utf-8"), connect_timeout=connect_timeout)
+        self._replica_id = self._store.get(REPLICA_ID_KEY).decode("utf-8")
+        self._logger = _StepLogger(self)
 
-        addr = self._store.get(MANAGER_ADDR_KEY).decode("utf-8")
-        self._client = ManagerClient(addr, connect_timeout=connect_timeout)
-        replica_id = self._store.get(REPLICA_ID_KEY).decode("utf-8")
-        self._replica_id = replica_id
-        self._logger = _ManagerLogger(manager=self, replica_id=replica_id or "", rank=rank)
-
-        self._step = 0
+        # ---- per-step state
+        self._view = _QuorumView()
+        self._ledger = _Ledger()
         self._quorum_id = -1
         self._errored: Optional[Exception] = None
         self._healing = False
+        self._pending_state_dict: Optional[Dict[str, object]] = None
         self._pending_work: List[torch.futures.Future[object]] = []
-        self._batches_committed = 0
-
-        self._participating_rank: Optional[int] = None
-        self._participating_world_size: int = 0
-        self._replica_rank: int = 0
-        self._replica_world_size: int = 0
+        self._executor = ThreadPoolExecutor(max_workers=1, thread_name_prefix="async_quorum")
+        self._quorum_future: Optional[_ThreadFuture] = None
 
         # Transports that can receive in place (NVLink) ask the manager for the live state.
         bind = getattr(self._checkpoint_transport, "bind_manager", None)
         if callable(bind):
             bind(self)
 
-    # ------------------------------------------------------------------ state dict plumbing
+    def _host_group_server(self, replica_id, lighthouse_addr, hostname, port, store, group_size, heartbeat_interval):
+        """Rank 0: starts the manager server of the replica group and publishes it in the group's store."""
+        unique_id = (replica_id or "") + str(uuid.uuid4())  # a restarted group is a new member for the lighthouse
+        listen_port = port if port is not None else int(os.environ.get(MANAGER_PORT_ENV, 0))
+        server = _ManagerServer(
+            replica_id=unique_id,
+            lighthouse_addr=_from_env(lighthouse_addr, "TORCHFT_LIGHTHOUSE"),
+            hostname=hostname,
+            bind=f"[::]:{listen_port}",
+            store_addr=store,
+            world_size=group_size,
+            heartbeat_interval=heartbeat_interval,
+            connect_timeout=self._connect_timeout,
+        )
+        self._store.set(MANAGER_ADDR_KEY, server.address())
+        self._store.set(REPLICA_ID_KEY, unique_id)
+        return server
+
+    # ------------------------------------------------------------------ lifecycle
     def set_state_dict_fns(self, load_state_dict: Callable[[T], None], state_dict: Callable[[], T]) -> None:
-        self._load_state_dict = load_state_dict
-        self._user_state_dict = state_dict
+        self._load_state_dict, self._user_state_dict = load_state_dict, state_dict
 
     def shutdown(self, wait: bool = True) -> None:
         """Stops the checkpoint transport, the manager server (rank 0) and the quorum thread."""
@@ -190,6 +226,31 @@ class Manager:
         self._executor.shutdown(wait=wait)
 
     # ------------------------------------------------------------------ collectives
+    def _collective(self, launch, result: T, what: str) -> "torch.futures.Future[T]":
+        """Common path of every cross-replica operation: wait for the quorum, skip once the step has
+        failed, start the operation, and turn any failure into ``report_error`` + ``result``."""
+        if self._errored is not None:
+            return _done(result)
+        self.wait_quorum()  # may itself surface a reconfiguration error
+        if self._errored is not None:
+            return _done(result)
+        try:
+            with trace_range(f"tft.{what}"):
+                participants = max(self.num_participants(), 1)
+                # a healing or spare replica is in the group but its data does not count
+                work = launch(self._pg, participants, self.is_participating())
+                finished = work.get_future()
+
+            def hand_back(f: "torch.futures.Future[object]") -> T:
+                f.value()
+                return result
+
+            return self.wrap_future(finished.then(hand_back), result)
+        except Exception as e:  # noqa: BLE001 - recorded, the step is discarded
+            self._logger.exception(f"got exception in {what} -- skipping remaining: {e}")
+            self.report_error(e)
+            return _done(result)
+
     def allreduce(self, tensor: torch.Tensor) -> "torch.futures.Future[torch.Tensor]":
         """Averages ``tensor`` in place over the participating replicas.
 
@@ -198,28 +259,9 @@ class Manager:
         immediately and the tensor contents must be considered garbage until the next
         successful step.
         """
-        if self.errored():
-            return _completed(tensor)
-        self.wait_quorum()
-        # wait_quorum may surface a reconfiguration error
-        if self.errored():
-            return _completed(tensor)
-        try:
-            with trace_range("tft.allreduce"):
-                n = self.num_participants()
-                # A healing or spare replica is in the group but adds zeros.
-                work = self._pg.allreduce_scaled(tensor, 1.0 / max(n, 1), contribute=self.is_participating())
-                fut = work.get_future()
-
-            def done(f: "torch.futures.Future[object]") -> torch.Tensor:
-                f.value()
-                return tensor
-
-            return self.wrap_future(fut.then(done), tensor)
-        except Exception as e:  # noqa: BLE001 - recorded, the step is discarded
-            self._logger.exception(f"got exception in all reduce -- skipping remaining: {e}")
-            self.report_error(e)
-            return _completed(tensor)
+        return self._collective(
+            lambda pg, n, contribute: pg.allreduce_scaled(tensor, 1.0 / n, contribute=contribute), tensor, "allreduce"
+        )
 
     def run_collective(self, launch, result: T) -> "torch.futures.Future[T]":
         """Runs a fused collective with the bookkeeping of ``allreduce``.
@@ -228,25 +270,7 @@ class Manager:
         returns its work object.  Waits for the quorum first, does nothing once the step has
         failed, and turns failures into ``report_error`` + ``result``.
         """
-        if self.errored():
-            return _completed(result)
-        self.wait_quorum()
-        if self.errored():
-            return _completed(result)
-        try:
-            with trace_range("tft.collective"):
-                work = launch(self._pg, max(self.num_participants(), 1), self.is_participating())
-                fut = work.get_future()
-
-            def done(f: "torch.futures.Future[object]") -> T:
-                f.value()
-                return result
-
-            return self.wrap_future(fut.then(done), result)
-        except Exception as e:  # noqa: BLE001 - recorded, the step is discarded
-            self._logger.exception(f"got exception in collective -- skipping remaining: {e}")
-            self.report_error(e)
-            return _completed(result)
+        return self._collective(launch, result, "collective")
 
     def report_error(self, e: Exception) -> None:
         """Marks the current step as failed; it will not commit and the group reconfigures."""
@@ -259,9 +283,8 @@ class Manager:
         self, fut: "torch.futures.Future[T]", default: T, timeout: Optional[timedelta] = None
     ) -> "torch.futures.Future[T]":
         """Adds a deadline to ``fut`` and converts failures into ``report_error`` + ``default``."""
-        fut = future_timeout(fut, timeout or self._timeout)
 
-        def callback(f: "torch.futures.Future[T]") -> T:
+        def absorb(f: "torch.futures.Future[T]") -> T:
             try:
                 return f.value()
             except Exception as e:  # noqa: BLE001 - recorded, the step is discarded
@@ -269,11 +292,11 @@ class Manager:
                 self.report_error(e)
                 return default
 
-        fut = fut.then(callback)
-        self._pending_work.append(cast("torch.futures.Future[object]", fut))
-        return fut
+        guarded = future_timeout(fut, timeout if timeout is not None else self._timeout).then(absorb)
+        self._pending_work.append(cast("torch.futures.Future[object]", guarded))
+        return guarded
 
-    # ------------------------------------------------------------------ quorum
+    # ------------------------------------------------------------------ quorum round
     def start_quorum(
         self, allow_heal: bool = True, shrink_only: bool = False, timeout: Optional[timedelta] = None
     ) -> None:
@@ -284,26 +307,26 @@ class Manager:
         in async mode loading is deferred to ``should_commit`` on the calling thread.
         """
         if self._quorum_future is not None:
-            self._quorum_future.result()
+            self._quorum_future.result()  # the previous round must be over
         # A failed step can leave the communicator out of step with its peers (one side gave up
         # on a collective the other side never started).  Ask for a fresh quorum id: every member
         # then reconfigures even though the membership is unchanged.
-        force_reconfigure = self._errored is not None
-        self._errored = None
-        self._healing = False
+        previous_step_failed = self._errored is not None
+        self._errored, self._healing = None, False
         self._quorum_future = self._executor.submit(
             self._async_quorum,
             allow_heal=allow_heal,
             shrink_only=shrink_only,
-            quorum_timeout=timeout or self._quorum_timeout,
-            force_reconfigure=force_reconfigure,
+            quorum_timeout=timeout if timeout is not None else self._quorum_timeout,
+            force_reconfigure=previous_step_failed,
         )
-        if not self._use_async_quorum:
-            self.wait_quorum()
-            if self._healing:
-                # The step can be joined right away because the state is loaded here.
-                self._apply_pending_state_dict()
-                self._healing = False
+        if self._use_async_quorum:
+            return
+        self.wait_quorum()
+        if self._healing:
+            # sync mode: the state is loaded here, on the caller's thread, so the step can be joined right away
+            self._apply_pending_state_dict()
+            self._healing = False
 
     def wait_quorum(self) -> None:
         """Blocks until the quorum, reconfiguration and checkpoint fetch of this step finished."""
@@ -313,83 +336,86 @@ class Manager:
     def _async_quorum(
         self, allow_heal: bool, shrink_only: bool, quorum_timeout: timedelta, force_reconfigure: bool = False
     ) -> None:
+        """One round on the worker thread: request, view, reconfiguration, recovery traffic."""
+        extra = {"force_reconfigure": True} if force_reconfigure else {}
         with trace_range("tft.quorum"):
-            kwargs = {"force_reconfigure": True} if force_reconfigure else {}
             quorum = self._client.quorum(
-                rank=self._rank,
-                step=self._step,
-                checkpoint_metadata=self._checkpoint_transport.metadata(),
-                shrink_only=shrink_only,
-                timeout=quorum_timeout,
-                **kwargs,
+                rank=self._rank, step=self._ledger.step, checkpoint_metadata=self._checkpoint_transport.metadata(),
+                shrink_only=shrink_only, timeout=quorum_timeout, **extra,
             )
-        max_step = quorum.max_step
-        self._replica_rank = quorum.replica_rank
-        self._replica_world_size = quorum.replica_world_size
-
-        # Async quorum or no healing: only the replicas at max_step contribute.
-        # Sync healing: everyone is up to date by the time gradients are exchanged.
-        if self._use_async_quorum or not allow_heal:
-            self._participating_rank, self._participating_world_size = quorum.max_rank, quorum.max_world_size
-        else:
-            self._participating_rank, self._participating_world_size = quorum.replica_rank, quorum.replica_world_size
-
-        if self._world_size_mode == WorldSizeMode.FIXED_WITH_SPARES:
-            self._participating_world_size = min(self._participating_world_size, self._min_replica_size)
-            if self._participating_rank is not None and self._participating_rank >= self._min_replica_size:
-                self._participating_rank = None
-
+        self._view = self._interpret(quorum, count_everyone=allow_heal and not self._use_async_quorum)
         if quorum.quorum_id != self._quorum_id:
-            prefixed = f"{quorum.store_address}/torchft/{quorum.quorum_id}/{self._rank}"
-            self._logger.info(f"reconfiguring for quorum_id={quorum.quorum_id} store_prefixed_addr={prefixed}")
-            with trace_range("tft.configure"):
-                # every member of the quorum is in the group, recovering ones included
-                self._pg.configure(prefixed, quorum.replica_rank, quorum.replica_world_size)
-            self._quorum_id = quorum.quorum_id
-
+            self._join_group(quorum)
         if not allow_heal:
             return
         if quorum.recover_dst_ranks:
-            self._logger.info(f"peers need recovery from us {quorum.recover_dst_ranks}")
-            with trace_range("tft.heal_send"):
-                self._checkpoint_transport.send_checkpoint(
-                    dst_ranks=quorum.recover_dst_ranks,
-                    step=max_step,
-                    state_dict=self._manager_state_dict(),
-                    timeout=self._timeout,
-                )
+            self._offer_state(quorum)
         if quorum.heal:
-            self._healing = True
-            src_addr = quorum.recover_src_manager_address
-            self._logger.info(f"healing required, fetching checkpoint metadata from {src_addr} max_step={max_step}")
-            with trace_range("tft.heal_recv"):
-                # The same local rank of the source group registered this metadata.
-                source = ManagerClient(src_addr, connect_timeout=self._connect_timeout)
-                metadata = source.checkpoint_metadata(self._rank, timeout=self._timeout)
-                assert quorum.recover_src_rank is not None, "must have a recover rank when healing"
-                self._logger.info(f"fetching checkpoint from rank {quorum.recover_src_rank} with metadata {metadata}")
-                # User state is only staged here: this is not the training thread.
-                self._pending_state_dict = cast(
-                    Dict[str, object],
-                    self._checkpoint_transport.recv_checkpoint(
-                        src_rank=quorum.recover_src_rank, metadata=metadata, step=max_step, timeout=self._timeout
-                    ),
-                )
-            self.load_state_dict(cast(Dict[str, int], self._pending_state_dict["torchft"]))
-            self._step = max_step
+            self._fetch_state(quorum)
+
+    def _interpret(self, quorum, count_everyone: bool) -> _QuorumView:
+        """Who contributes this step.  With synchronous healing every member is up to date by the time
+        data is exchanged, so all of them count; otherwise only the members at the newest step do."""
+        view = _QuorumView(replica_rank=quorum.replica_rank, replica_world=quorum.replica_world_size)
+        if count_everyone:
+            view.active_rank, view.active_world = quorum.replica_rank, quorum.replica_world_size
+        else:
+            view.active_rank, view.active_world = quorum.max_rank, quorum.max_world_size
+        if self._world_size_mode == WorldSizeMode.FIXED_WITH_SPARES:
+            cap = self._min_replica_size
+            view.active_world = min(view.active_world, cap)
+            if view.active_rank is not None and view.active_rank >= cap:
+                view.active_rank = None  # a hot spare: receives the result, contributes nothing
+        return view
+
+    def _join_group(self, quorum) -> None:
+        """Membership changed: point the process group at the new peers (recovering ones included)."""
+        rendezvous = f"{quorum.store_address}/torchft/{quorum.quorum_id}/{self._rank}"
+        self._logger.info(f"reconfiguring for quorum_id={quorum.quorum_id} store_prefixed_addr={rendezvous}")
+        with trace_range("tft.configure"):
+            self._pg.configure(rendezvous, quorum.replica_rank, quorum.replica_world_size)
+        self._quorum_id = quorum.quorum_id
+
+    def _offer_state(self, quorum) -> None:
+        """Peers that are behind were assigned to this replica: let them read the live state."""
+        self._logger.info(f"peers need recovery from us {quorum.recover_dst_ranks}")
+        with trace_range("tft.heal_send"):
+            self._checkpoint_transport.send_checkpoint(
+                dst_ranks=quorum.recover_dst_ranks, step=quorum.max_step, state_dict=self._manager_state_dict(),
+                timeout=self._timeout,
+            )
+
+    def _fetch_state(self, quorum) -> None:
+        """This replica is behind: fetch the state of its assigned source and stage it."""
+        self._healing = True
+        source_addr, source_rank, version = quorum.recover_src_manager_address, quorum.recover_src_rank, quorum.max_step
+        self._logger.info(f"healing required, fetching checkpoint metadata from {source_addr} max_step={version}")
+        assert source_rank is not None, "must have a recover rank when healing"
+        with trace_range("tft.heal_recv"):
+            # the same local rank of the source group registered the metadata we need
+            peer = ManagerClient(source_addr, connect_timeout=self._connect_timeout)
+            where = peer.checkpoint_metadata(self._rank, timeout=self._timeout)
+            self._logger.info(f"fetching checkpoint from rank {source_rank} with metadata {where}")
+            staged = self._checkpoint_transport.recv_checkpoint(
+                src_rank=source_rank, metadata=where, step=version, timeout=self._timeout
+            )
+        # User state is only staged: this is not the training thread.  The counters can move now.
+        self._pending_state_dict = cast(Dict[str, object], staged)
+        self.load_state_dict(cast(Dict[str, int], self._pending_state_dict["torchft"]))
+        self._ledger.step = version
 
     def _apply_pending_state_dict(self) -> None:
         assert self._healing, "must be in healing state"
         assert self._quorum_future is not None, "must call step before should_commit"
         self._quorum_future.result()
-        self._logger.info("applying pending state dict")
-        assert self._pending_state_dict is not None, "checkpoint was not staged"
+        staged, self._pending_state_dict = self._pending_state_dict, None
+        assert staged is not None, "checkpoint was not staged"
         assert self._load_state_dict is not None, "user load_state_dict is not initialized."
-        self._load_state_dict(cast(T, self._pending_state_dict["user"]))  # type: ignore[misc]
-        self._pending_state_dict = None
+        self._logger.info("applying pending state dict")
+        self._load_state_dict(cast(T, staged["user"]))  # type: ignore[misc]
         self._logger.info("Loaded state dict.")
 
-    # ------------------------------------------------------------------ commit
+    # ------------------------------------------------------------------ vote
     def should_commit(self, timeout: Optional[timedelta] = None) -> bool:
         """Group-wide vote on whether the optimizer may step.  Call once per step on every rank.
 
@@ -397,59 +423,56 @@ class Manager:
         then asks the manager server, which answers True only if every rank of the
         replica group voted True.  Different replica groups may decide differently.
         """
-        for work in self._pending_work:
+        outstanding, self._pending_work = self._pending_work, []
+        for work in outstanding:
             if self._errored is not None:
                 break  # the step is lost already
             work.wait()
-        self._pending_work = []
-
         if self._healing:
             self._apply_pending_state_dict()
 
-        enough_replicas = self.num_participants() >= self._min_replica_size
-        local_should_commit = enough_replicas and self._errored is None
-        should_commit = self._client.should_commit(
-            self._rank, self._step, local_should_commit, timeout=timeout or self._timeout
+        participants = self.num_participants()
+        quorate = participants >= self._min_replica_size
+        my_vote = quorate and self._errored is None
+        decision = self._client.should_commit(
+            self._rank, self._ledger.step, my_vote, timeout=timeout if timeout is not None else self._timeout
         )
-        self._logger.info(
-            f"should_commit={should_commit} enough_replicas={enough_replicas}, errored={self._errored}"
-        )
+        self._logger.info(f"should_commit={decision} enough_replicas={quorate}, errored={self._errored}")
         # From here on the weights may change, so peers must not read them any more.
         self._checkpoint_transport.disallow_checkpoint()
-        if should_commit:
-            self._step += 1
-            self._batches_committed += self.num_participants()
-        return should_commit
+        if decision:
+            self._ledger.commit(participants)
+        return decision
 
-    # ------------------------------------------------------------------ state
+    # ------------------------------------------------------------------ state and accessors
     def load_state_dict(self, state_dict: Dict[str, int]) -> None:
-        self._step = state_dict["step"]
-        self._batches_committed = state_dict["batches_committed"]
-
-    def _manager_state_dict(self) -> Dict[str, object]:
-        assert self._user_state_dict is not None, "user state_dict is not initialized."
-        return {"user": self._user_state_dict(), "torchft": self.state_dict()}
+        self._ledger = _Ledger(step=state_dict["step"], batches=state_dict["batches_committed"])
 
     def state_dict(self) -> Dict[str, int]:
         """Must be saved with (and restored from) every durable checkpoint."""
-        return {"step": self._step, "batches_committed": self._batches_committed}
+        return self._ledger.as_dict()
+
+    def _manager_state_dict(self) -> Dict[str, object]:
+        """What a recovering peer receives: the user's state plus the counters above."""
+        assert self._user_state_dict is not None, "user state_dict is not initialized."
+        return {"user": self._user_state_dict(), "torchft": self.state_dict()}
 
     def current_step(self) -> int:
         """Number of committed steps (optimizer steps); also the live-recovery version."""
-        return self._step
+        return self._ledger.step
 
     def batches_committed(self) -> int:
         """Total batches committed over all replica groups and steps (sum of participants per step)."""
-        return self._batches_committed
+        return self._ledger.batches
 
     def num_participants(self) -> int:
         """Replicas contributing to the current step (the averaging divisor)."""
-        assert self._participating_world_size >= 0, "internal error"
-        return self._participating_world_size
+        assert self._view.active_world >= 0, "internal error"
+        return self._view.active_world
 
     def is_participating(self) -> bool:
         """False for spares and for a replica that is still healing in async mode."""
-        if self._participating_rank is None:
+        if self._view.active_rank is None:
             return False
         if self._healing:
             assert self._use_async_quorum
@@ -458,38 +481,31 @@ class Manager:
 
     def replica_rank(self) -> int:
         """Rank of this replica group within the current quorum (all members, recovering included)."""
-        return self._replica_rank
+        return self._view.replica_rank
 
     def replica_world_size(self) -> int:
-        return self._replica_world_size
+        return self._view.replica_world
 
     def replica_id(self) -> str:
         return self._replica_id
 
 
-def _completed(value: T) -> "torch.futures.Future[T]":
-    fut: torch.futures.Future = torch.futures.Future()
-    fut.set_result(value)
-    return fut
+class _StepLogger:
+    """Log lines of a manager carry ``[replica_id/rank - step N]`` in front."""
 
+    def __init__(self, manager: Manager) -> None:
+        self._log = logging.getLogger(__name__)
+        self._owner = manager
 
-class _ManagerLogger:
-    """Prefixes log lines with ``[replica_id/rank - step N]``."""
-
-    def __init__(self, manager: Manager, replica_id: str, rank: int) -> None:
-        self._logger = logging.getLogger(__name__)
-        self._replica_id = replica_id
-        self._rank = rank
-        self._manager = manager
-
-    def prefix(self) -> str:
-        return f"[{self._replica_id}/{self._rank} - step {self._manager.current_step()}]"
+    def _line(self, msg: str) -> str:
+        m = self._owner
+        return f"[{m._replica_id}/{m._rank} - step {m.current_step()}] {msg}"
 
     def info(self, msg: str) -> None:
-        self._logger.info(f"{self.prefix()} {msg}")
+        self._log.info(self._line(msg))
 
     def warn(self, msg: str) -> None:
-        self._logger.warning(f"{self.prefix()} {msg}")
+        self._log.warning(self._line(msg))
 
     def exception(self, msg: str) -> None:
-        self._logger.exception(f"{self.prefix()} {msg}")
+        self._log.exception(self._line(msg))
