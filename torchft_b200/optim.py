@@ -4,47 +4,59 @@
 update only when the replica group voted to commit, so a step that hit a communication
 error leaves the weights untouched.  Same contract as the reference's
 ``torchft/optim.py:24-63``.
+
+Everything else an optimizer offers (``param_groups``, ``state``, ``state_dict``,
+``load_state_dict``, ``add_param_group``, hooks, LR-scheduler access, ...) is forwarded to the
+wrapped optimizer, so schedulers and checkpoint code keep working on the wrapper.
 """
 
 from __future__ import annotations
 
-from typing import TYPE_CHECKING, Any, Dict, List, Mapping, Optional
+from typing import TYPE_CHECKING, Any, Optional
 
-import torch
 from torch.optim import Optimizer
 
 if TYPE_CHECKING:
     from torchft_b200.manager import Manager
 
+# names that live on the wrapper itself (an LR scheduler re-binds ``step`` on the object it is given);
+# all other reads and writes go to the wrapped optimizer
+_OWN = frozenset(("optim", "manager", "step", "zero_grad"))
+
 
 class OptimizerWrapper(Optimizer):
+    """``Optimizer`` in the sense of ``isinstance`` (LR schedulers check that), a proxy otherwise."""
+
     def __init__(self, manager: "Manager", optim: Optimizer) -> None:
-        # Optimizer.__init__ is skipped on purpose: every attribute proxies ``optim``.
-        self.optim = optim
-        self.manager = manager
+        # Optimizer.__init__ is skipped on purpose: there is no state of our own to set up.
+        object.__setattr__(self, "optim", optim)
+        object.__setattr__(self, "manager", manager)
 
-    def add_param_group(self, param_group: Dict[str, Any]) -> None:
-        self.optim.add_param_group(param_group)
-
-    def load_state_dict(self, state_dict: Mapping[str, Any]) -> None:
-        self.optim.load_state_dict(state_dict)  # type: ignore[arg-type]
-
-    def state_dict(self) -> Dict[str, Any]:
-        return self.optim.state_dict()
-
+    # ---- the two calls that carry the protocol
     def zero_grad(self, set_to_none: bool = True) -> None:
+        """Start of a step: the quorum is requested before the gradients are cleared."""
         self.manager.start_quorum()
         self.optim.zero_grad(set_to_none)
 
     def step(self, closure: Optional[object] = None) -> None:
-        assert closure is None, "optimizers that use closures are not supported"
-        if self.manager.should_commit():
-            self.optim.step()
+        """End of a step: the update happens only if the replica group votes to commit."""
+        if closure is not None:
+            raise AssertionError("optimizers that use closures are not supported")
+        if not self.manager.should_commit():
+            return
+        self.optim.step()
 
-    @property
-    def param_groups(self) -> List[Dict[str, Any]]:  # type: ignore[override]
-        return self.optim.param_groups
+    # ---- everything else belongs to the wrapped optimizer
+    def __getattribute__(self, name: str) -> Any:
+        if name in _OWN or (name.startswith("__") and name.endswith("__")):
+            return object.__getattribute__(self, name)
+        return getattr(object.__getattribute__(self, "optim"), name)
 
-    @property
-    def state(self) -> Mapping[torch.Tensor, Any]:  # type: ignore[override]
-        return self.optim.state
+    def __setattr__(self, name: str, value: Any) -> None:
+        if name in _OWN:
+            object.__setattr__(self, name, value)
+        else:
+            setattr(self.optim, name, value)
+
+    def __repr__(self) -> str:
+        return f"OptimizerWrapper({self.optim!r})"
