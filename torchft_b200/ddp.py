@@ -6,12 +6,13 @@ errors recorded instead of raised).  ``PureDistributedDataParallel`` is the hook
 variant without buckets.  Parity: the reference's ``torchft/ddp.py:32-97``.
 """
 
-from typing import TYPE_CHECKING
+from typing import TYPE_CHECKING, Any, List
 
 import torch
-import torch.distributed as dist
 from torch import nn
-from torch.nn import parallel
+from torch.distributed import GradBucket
+from torch.nn.parallel import DistributedDataParallel as _TorchDDP
+from torch.utils.hooks import RemovableHandle
 
 from torchft_b200.process_group import ProcessGroupDummy
 
@@ -19,7 +20,15 @@ if TYPE_CHECKING:
     from torchft_b200.manager import Manager
 
 
-class DistributedDataParallel(parallel.DistributedDataParallel):
+def _reduce_bucket(manager: "Manager", bucket: GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """DDP communication hook: one flat bucket, averaged over the live replica groups, in place.
+
+    torch inspects the annotations of a hook at registration, so they are real objects, not strings.
+    """
+    return manager.allreduce(bucket.buffer())
+
+
+class DistributedDataParallel(_TorchDDP):
     """torch DDP whose gradient communication goes through a ``Manager``.
 
     The module itself is built on a world-size-1 dummy group, so the constructor's
@@ -29,34 +38,39 @@ class DistributedDataParallel(parallel.DistributedDataParallel):
     exactly the same buckets as the ones already training.
     """
 
-    def __init__(self, manager: "Manager", module: nn.Module, **kwargs: object) -> None:
-        pg = ProcessGroupDummy(0, 1)
-        super().__init__(
-            module,
-            process_group=pg,
-            find_unused_parameters=True,  # keeps the first bucket assignment for good
-            **kwargs,  # type: ignore[arg-type]
-        )
-        self.register_comm_hook(manager, self._comm_hook)
-
-    @staticmethod
-    def _comm_hook(state: "Manager", bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
-        return state.allreduce(bucket.buffer())
+    def __init__(self, manager: "Manager", module: nn.Module, **kwargs: Any) -> None:
+        kwargs["process_group"] = ProcessGroupDummy(0, 1)
+        kwargs["find_unused_parameters"] = True  # keeps the first bucket assignment for good
+        super().__init__(module, **kwargs)
+        self.register_comm_hook(manager, _reduce_bucket)
 
 
 class PureDistributedDataParallel(nn.Module):
-    """Per-parameter allreduce from ``post_accumulate_grad`` hooks; no buckets, no reducer."""
+    """Per-parameter allreduce from ``post_accumulate_grad`` hooks; no buckets, no reducer.
+
+    Each gradient is handed to the manager the moment autograd has finished accumulating it, so
+    communication overlaps the rest of the backward pass; ``Manager.should_commit`` waits for all of it.
+    """
 
     def __init__(self, manager: "Manager", module: nn.Module) -> None:
         super().__init__()
         self.module = module
+        self._handles: List[RemovableHandle] = []
 
-        def post_grad_hook(p: torch.Tensor) -> None:
-            if p.grad is not None:
-                manager.allreduce(p.grad)
+        def reduce_when_ready(param: torch.Tensor) -> None:
+            grad = param.grad
+            if grad is None:
+                return
+            manager.allreduce(grad)
 
-        for p in module.parameters():
-            p.register_post_accumulate_grad_hook(post_grad_hook)
+        for param in module.parameters():
+            if param.requires_grad:
+                self._handles.append(param.register_post_accumulate_grad_hook(reduce_when_ready))
 
-    def forward(self, *args: object) -> object:
-        return self.module(*args)
+    def remove_hooks(self) -> None:
+        """Detaches the gradient hooks (the wrapped module then trains without communication)."""
+        while self._handles:
+            self._handles.pop().remove()
+
+    def forward(self, *args: Any, **kwargs: Any) -> Any:
+        return self.module(*args, **kwargs)

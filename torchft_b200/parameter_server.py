@@ -8,7 +8,7 @@ involved.  Subclasses provide ``new_process_group()`` and ``forward(session_id, 
 
 Parity: the reference's ``torchft/parameter_server.py:31-195`` (prototype there, too).
 Unlike the reference the session runs in a dedicated thread instead of occupying the
-HTTP handler thread.
+HTTP handler thread, and the server keeps a table of the sessions that are open.
 """
 
 from __future__ import annotations
@@ -20,7 +20,9 @@ import threading
 import urllib.request
 import uuid
 from abc import ABC, abstractmethod
+from dataclasses import dataclass, field
 from http.server import BaseHTTPRequestHandler
+from typing import Dict, Type
 
 from torch.distributed import TCPStore
 
@@ -29,55 +31,93 @@ from torchft_b200.process_group import ProcessGroup
 
 logger: logging.Logger = logging.getLogger(__name__)
 
+_SESSION_PATH = "/new_session"
+_SERVER_RANK, _CLIENT_RANK, _SESSION_WORLD = 0, 1, 2
+
+
+@dataclass
+class _Session:
+    """One client's rendezvous point: an id and the store prefix both ends configure on."""
+
+    store_addr: str
+    ident: str = field(default_factory=lambda: str(uuid.uuid4()))
+
+    def announcement(self) -> bytes:
+        return (json.dumps({"session_id": self.ident, "store_addr": self.store_addr}) + "\n").encode()
+
+
+def _handler_for(ps: "ParameterServer") -> Type[BaseHTTPRequestHandler]:
+    """HTTP front end of one server: answers the session request, then hands the session to a thread."""
+
+    class _Handler(BaseHTTPRequestHandler):
+        def _reply(self, status: int, content_type: str, body: bytes) -> None:
+            self.send_response(status)
+            self.send_header("Content-type", content_type)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+            self.wfile.flush()
+
+        def do_GET(self) -> None:  # noqa: N802 - http.server API
+            if self.path != _SESSION_PATH:
+                self._reply(400, "text/plain", f"invalid path, got {self.path}".encode())
+                return
+            session = ps._open_session()
+            self._reply(200, "application/json", session.announcement())
+            ps._run_in_thread(session)
+
+        def log_message(self, fmt: str, *args: object) -> None:
+            logger.debug(fmt % args)
+
+    return _Handler
+
 
 class ParameterServer(ABC):
     def __init__(self, port: int, store_port: int = 0) -> None:
-        """
-        Args:
-            port: HTTP port (0 picks a free one)
-            store_port: TCPStore port (0 picks a free one)
-        """
+        """``port`` is the HTTP port and ``store_port`` the TCPStore port; 0 picks a free one for either."""
         self.store = TCPStore(host_name="0.0.0.0", port=store_port, is_master=True, wait_for_workers=False)
-        ps = self
-
-        class RequestHandler(BaseHTTPRequestHandler):
-            def do_GET(self) -> None:  # noqa: N802 - http.server API
-                if self.path != "/new_session":
-                    self.send_response(400)
-                    self.send_header("Content-type", "text/plain")
-                    self.end_headers()
-                    self.wfile.write(f"invalid path, got {self.path}".encode())
-                    return
-                session_id = str(uuid.uuid4())
-                host = advertised_host(socket.gethostname())
-                store_addr = f"{host}:{ps.store.port}/session/{session_id}"
-                logger.info(f"creating new session {session_id}")
-                body = (json.dumps({"session_id": session_id, "store_addr": store_addr}) + "\n").encode()
-                self.send_response(200)
-                self.send_header("Content-type", "application/json")
-                self.send_header("Content-Length", str(len(body)))
-                self.end_headers()
-                self.wfile.write(body)
-                self.wfile.flush()
-                threading.Thread(
-                    target=ps._handle_session,
-                    args=(session_id, store_addr),
-                    daemon=True,
-                    name=f"tft_ps_session_{session_id[:8]}",
-                ).start()
-
-            def log_message(self, fmt: str, *args: object) -> None:
-                logger.debug(fmt % args)
-
-        self._server = make_http_server(port, RequestHandler)
-        logger.info(f"Started ParameterServer on {self.address()}...")
+        self._host = advertised_host(socket.gethostname())
+        self._sessions: Dict[str, _Session] = {}
+        self._sessions_lock = threading.Lock()
+        self._server = make_http_server(port, _handler_for(self))
         self._thread = threading.Thread(target=self._serve, daemon=True, name="tft_parameter_server")
         self._thread.start()
+        logger.info(f"Started ParameterServer on {self.address()}...")
 
+    # ------------------------------------------------------------------ to be provided by the subclass
+    @classmethod
+    @abstractmethod
+    def new_process_group(cls) -> ProcessGroup:
+        """Returns a new, not yet configured process group (server and client both call this)."""
+
+    @abstractmethod
+    def forward(self, session_id: str, pg: ProcessGroup) -> None:
+        """Runs once per session in its own thread (server is rank 0, client rank 1).
+
+        Loop inside for several operations per session.  On an exception the group is
+        dropped and the client has to open a new session.
+        """
+
+    # ------------------------------------------------------------------ client side
+    @classmethod
+    def new_session(cls, address: str) -> ProcessGroup:
+        """Opens a session at ``address`` and returns the configured group (the client is rank 1)."""
+        with urllib.request.urlopen(address) as response:
+            offer = json.load(response)
+        logger.info(f"connecting to session {offer['session_id']} at {offer['store_addr']}")
+        group = cls.new_process_group()
+        group.configure(offer["store_addr"], rank=_CLIENT_RANK, world_size=_SESSION_WORLD)
+        return group
+
+    # ------------------------------------------------------------------ server side
     def address(self) -> str:
         """``http://host:port/new_session``"""
-        port = self._server.socket.getsockname()[1]
-        return f"http://{advertised_host(socket.gethostname())}:{port}/new_session"
+        return f"http://{self._host}:{self._server.socket.getsockname()[1]}{_SESSION_PATH}"
+
+    def open_sessions(self) -> int:
+        """Number of sessions whose ``forward`` has not returned yet."""
+        with self._sessions_lock:
+            return len(self._sessions)
 
     def shutdown(self) -> None:
         self._server.shutdown()
@@ -89,35 +129,29 @@ class ParameterServer(ABC):
         except Exception:  # noqa: BLE001
             logger.exception("got exception in parameter server")
 
-    @classmethod
-    @abstractmethod
-    def new_process_group(cls) -> ProcessGroup:
-        """Returns a new, not yet configured process group (server and client both call this)."""
+    def _open_session(self) -> _Session:
+        session = _Session(store_addr="")
+        session.store_addr = f"{self._host}:{self.store.port}/session/{session.ident}"
+        with self._sessions_lock:
+            self._sessions[session.ident] = session
+        logger.info(f"creating new session {session.ident}")
+        return session
 
-    @classmethod
-    def new_session(cls, address: str) -> ProcessGroup:
-        """Client side: opens a session at ``address`` and returns the configured group (client is rank 1)."""
-        with urllib.request.urlopen(address) as f:
-            data = json.load(f)
-        session_id = data["session_id"]
-        store_addr = data["store_addr"]
-        logger.info(f"connecting to session {session_id} at {store_addr}")
-        pg = cls.new_process_group()
-        pg.configure(store_addr, rank=1, world_size=2)
-        return pg
+    def _run_in_thread(self, session: _Session) -> None:
+        threading.Thread(
+            target=self._handle_session,
+            args=(session.ident, session.store_addr),
+            daemon=True,
+            name=f"tft_ps_session_{session.ident[:8]}",
+        ).start()
 
     def _handle_session(self, session_id: str, store_addr: str) -> None:
         try:
-            pg = self.new_process_group()
-            pg.configure(store_addr, rank=0, world_size=2)
-            self.forward(session_id, pg)
+            group = self.new_process_group()
+            group.configure(store_addr, rank=_SERVER_RANK, world_size=_SESSION_WORLD)
+            self.forward(session_id, group)
         except Exception:  # noqa: BLE001 - only this session is lost
             logger.exception(f"session {session_id} failed")
-
-    @abstractmethod
-    def forward(self, session_id: str, pg: ProcessGroup) -> None:
-        """Runs once per session in its own thread (server is rank 0, client rank 1).
-
-        Loop inside for several operations per session.  On an exception the group is
-        dropped and the client has to open a new session.
-        """
+        finally:
+            with self._sessions_lock:
+                self._sessions.pop(session_id, None)
