@@ -236,3 +236,39 @@ def test_durable_checkpoint_round_trip(tmp_path):
     assert out["user"]["rank"] == 1 and out["dataloader"] == {"position": 70}
     assert torch.equal(out["user"]["model"]["weight"], model.state_dict()["weight"])
     assert load_checkpoint(str(tmp_path / "nothing"), restored) is None
+
+
+def test_checkpoint_gate_counts_readers_and_close_waits_for_them():
+    """Two peers stream at once; closing the gate returns only after both have left."""
+    from torchft_b200.checkpointing import _Gate
+
+    gate = _Gate()
+    with pytest.raises(TimeoutError):
+        with gate.reading(timedelta(seconds=0.05)):
+            pass
+    gate.open(5, {"w": 1})
+    inside = threading.Barrier(3)
+    leave = threading.Event()
+    seen = []
+
+    def reader():
+        with gate.reading(timedelta(seconds=5)) as (step, state):
+            seen.append((step, state["w"]))
+            inside.wait(timeout=5)
+            leave.wait(timeout=5)
+
+    readers = [threading.Thread(target=reader) for _ in range(2)]
+    for t in readers:
+        t.start()
+    inside.wait(timeout=5)  # both readers are in at the same time
+    closed = threading.Event()
+    closer = threading.Thread(target=lambda: (gate.close(), closed.set()))
+    closer.start()
+    time.sleep(0.1)
+    assert not closed.is_set()  # readers still streaming
+    leave.set()
+    closer.join(timeout=5)
+    assert closed.is_set() and seen == [(5, 1), (5, 1)]
+    with pytest.raises(TimeoutError):
+        with gate.reading(timedelta(seconds=0.05)):
+            pass

@@ -10,8 +10,10 @@ the gate for a step and fail once ``disallow_checkpoint`` closed it again, so th
 weights cannot be read while the optimizer mutates them.
 
 Interface, URL scheme, status codes and message texts follow the reference's
-``torchft/checkpointing.py:34-270``; the NVLink peer-to-peer transport for GPUs of one
-NVSwitch domain lives in ``torchft_b200.parallel.nvlink_heal``.
+``torchft/checkpointing.py:34-270``; the gate here is a reader count under a condition
+variable (several peers can be served at once, closing waits for all of them) where the
+reference holds one lock.  The NVLink peer-to-peer transport for GPUs of one NVSwitch
+domain lives in ``torchft_b200.parallel.nvlink_heal``.
 """
 
 from __future__ import annotations
@@ -20,12 +22,13 @@ import io
 import logging
 import socket
 import threading
+import time
 import urllib.request
 from abc import ABC, abstractmethod
 from contextlib import contextmanager
 from datetime import timedelta
 from http.server import BaseHTTPRequestHandler
-from typing import Dict, Generator, Generic, List, Optional, TypeVar
+from typing import Dict, Generator, Generic, Iterator, List, Optional, Tuple, Type, TypeVar
 
 import torch
 
@@ -34,6 +37,8 @@ from torchft_b200.http import advertised_host, make_http_server
 logger: logging.Logger = logging.getLogger(__name__)
 
 T = TypeVar("T")
+
+_URL_PREFIX = "/checkpoint/"
 
 
 def _compact(state: object) -> object:
@@ -99,90 +104,111 @@ def _timed_acquire(lock: threading.Lock, timeout: timedelta) -> Generator[None, 
         lock.release()
 
 
+class _Gate(Generic[T]):
+    """What may be served right now: nothing (closed), or one state dict of one step (open).
+
+    Readers enter with ``reading()``; they wait while the gate is closed and are counted while
+    they stream.  ``close()`` returns only when the last reader has left, which is what lets the
+    caller change the weights afterwards.
+    """
+
+    def __init__(self) -> None:
+        self._cond = threading.Condition()
+        self._open = False
+        self._readers = 0
+        self._step = -1
+        self._payload: Optional[T] = None
+
+    def open(self, step: int, payload: T) -> None:
+        with self._cond:
+            self._step, self._payload, self._open = step, payload, True
+            self._cond.notify_all()
+
+    def close(self) -> None:
+        with self._cond:
+            self._open = False
+            while self._readers:
+                self._cond.wait()
+
+    @contextmanager
+    def reading(self, timeout: timedelta) -> Iterator[Tuple[int, Optional[T]]]:
+        deadline = time.monotonic() + timeout.total_seconds()
+        with self._cond:
+            while not self._open:
+                left = deadline - time.monotonic()
+                if left <= 0:
+                    raise TimeoutError(f"timed out waiting for a checkpoint to be allowed after {timeout}")
+                self._cond.wait(left)
+            self._readers += 1
+            served = (self._step, self._payload)
+        try:
+            yield served
+        finally:
+            with self._cond:
+                self._readers -= 1
+                self._cond.notify_all()
+
+
+def _checkpoint_handler(gate: "_Gate[object]", timeout: timedelta) -> Type[BaseHTTPRequestHandler]:
+    """Request handler of one ``CheckpointServer``."""
+    socket_timeout = timeout.total_seconds()
+
+    class _Handler(BaseHTTPRequestHandler):
+        timeout = socket_timeout  # per-connection socket timeout
+
+        def _head(self, status: int, content_type: str) -> None:
+            self.send_response(status)
+            self.send_header("Content-type", content_type)
+            self.end_headers()
+
+        def do_GET(self) -> None:  # noqa: N802 - http.server API
+            try:
+                with gate.reading(timeout) as (step, state):
+                    if self.path != f"{_URL_PREFIX}{step}":
+                        self._head(400, "text/plain")
+                        self.wfile.write(f"invalid checkpoint requested, serving {step} but got {self.path}".encode())
+                        return
+                    self._head(200, "application/octet-stream")
+                    torch.save(_compact(state), self.wfile)
+            except Exception as e:  # noqa: BLE001 - reported to the client
+                logger.exception(f"exception while serving checkpoint: {e}")
+                try:
+                    self._head(500, "text/plain")
+                    self.wfile.write(str(e).encode())
+                except Exception:  # noqa: BLE001 - peer already gone
+                    pass
+
+        def log_message(self, fmt: str, *args: object) -> None:
+            logger.debug(fmt % args)
+
+    return _Handler
+
+
 class CheckpointServer(CheckpointTransport[T]):
-    """HTTP transport; one server per rank, started on an ephemeral port."""
+    """HTTP transport; one server per rank, started on an ephemeral port with the gate closed."""
 
     def __init__(self, timeout: timedelta) -> None:
-        # The gate lock is HELD while serving is disallowed.
-        self._checkpoint_lock = threading.Lock()
-        self._disallowed = False
-        self._step = -1
         self._timeout = timeout
-        self._state_dict: Optional[T] = None
+        self._gate: _Gate[T] = _Gate()
         self._stopped = False
-        self.disallow_checkpoint()
-
-        transport = self
-
-        class RequestHandler(BaseHTTPRequestHandler):
-            timeout = transport._timeout.total_seconds()  # per-connection socket timeout
-
-            def do_GET(self) -> None:  # noqa: N802 - http.server API
-                try:
-                    with _timed_acquire(transport._checkpoint_lock, transport._timeout):
-                        step = transport._step
-                        prefix = "/checkpoint/"
-                        if self.path != f"{prefix}{step}":
-                            self.send_response(400)
-                            self.send_header("Content-type", "text/plain")
-                            self.end_headers()
-                            self.wfile.write(
-                                f"invalid checkpoint requested, serving {step} but got {self.path}".encode()
-                            )
-                            return
-                        self.send_response(200)
-                        self.send_header("Content-type", "application/octet-stream")
-                        self.end_headers()
-                        torch.save(_compact(transport._state_dict), self.wfile)
-                except Exception as e:  # noqa: BLE001 - reported to the client
-                    logger.exception(f"exception while serving checkpoint: {e}")
-                    try:
-                        self.send_response(500)
-                        self.send_header("Content-type", "text/plain")
-                        self.end_headers()
-                        self.wfile.write(str(e).encode())
-                    except Exception:  # noqa: BLE001 - peer already gone
-                        pass
-
-            def log_message(self, fmt: str, *args: object) -> None:
-                logger.debug(fmt % args)
-
-        self._server = make_http_server(0, RequestHandler)
-        logger.info(f"checkpoint server listening on {self.address()}")
+        self._server = make_http_server(0, _checkpoint_handler(self._gate, timeout))  # type: ignore[arg-type]
         self._thread = threading.Thread(target=self._serve, daemon=True, name="tft_checkpoint_server")
         self._thread.start()
+        logger.info(f"checkpoint server listening on {self.address()}")
 
-    @classmethod
-    def load_from_address(cls, address: str, timeout: timedelta) -> T:
-        """Streams and unpickles the checkpoint at ``address``."""
-        logger.info(f"fetching checkpoint from {address}")
-        with urllib.request.urlopen(address, timeout=timeout.total_seconds()) as f:
-            # torch.load needs a seekable file; a buffered read of the stream keeps one copy.
-            data = io.BytesIO(f.read())
-        # Non-tensor state (schedulers, counters, ...) is allowed, hence weights_only=False.
-        return torch.load(data, weights_only=False)
+    # ---- CheckpointTransport
+    def metadata(self) -> str:
+        return self.address()
 
-    def address(self) -> str:
-        """``http://<host>:<port>/checkpoint/`` -- append the step to fetch."""
-        port = self._server.socket.getsockname()[1]
-        return f"http://{advertised_host(socket.gethostname())}:{port}/checkpoint/"
-
-    def _serve(self) -> None:
-        try:
-            self._server.serve_forever()
-        except Exception as e:  # noqa: BLE001
-            logger.exception(f"checkpoint server crashed: {e}")
+    def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
+        # Nothing is pushed: the state dict is served by reference while the gate is open.
+        self._gate.open(step, state_dict)
 
     def disallow_checkpoint(self) -> None:
-        if not self._disallowed:
-            self._disallowed = True
-            self._checkpoint_lock.acquire()
+        self._gate.close()
 
-    def allow_checkpoint(self, step: int) -> None:
-        self._step = step
-        if self._disallowed:
-            self._disallowed = False
-            self._checkpoint_lock.release()
+    def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
+        return self.load_from_address(f"{metadata}{step}", timeout)
 
     def shutdown(self, wait: bool = True) -> None:
         if self._stopped:
@@ -195,13 +221,28 @@ class CheckpointServer(CheckpointTransport[T]):
             threading.Thread(target=self._server.shutdown, daemon=True).start()
         self._server.server_close()
 
-    def metadata(self) -> str:
-        return self.address()
+    # ---- HTTP specifics
+    def allow_checkpoint(self, step: int) -> None:
+        """Re-opens the gate for ``step`` with the state dict given to the last ``send_checkpoint``."""
+        self._gate.open(step, self._gate._payload)  # noqa: SLF001
 
-    def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
-        # Nothing is pushed: the state dict is served by reference while the gate is open.
-        self._state_dict = state_dict
-        self.allow_checkpoint(step)
+    def address(self) -> str:
+        """``http://<host>:<port>/checkpoint/`` -- append the step to fetch."""
+        host = advertised_host(socket.gethostname())
+        return f"http://{host}:{self._server.socket.getsockname()[1]}{_URL_PREFIX}"
 
-    def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
-        return self.load_from_address(f"{metadata}{step}", timeout)
+    @classmethod
+    def load_from_address(cls, address: str, timeout: timedelta) -> T:
+        """Streams and unpickles the checkpoint at ``address``."""
+        logger.info(f"fetching checkpoint from {address}")
+        with urllib.request.urlopen(address, timeout=timeout.total_seconds()) as response:
+            # torch.load needs a seekable file; a buffered read of the stream keeps one copy.
+            blob = io.BytesIO(response.read())
+        # Non-tensor state (schedulers, counters, ...) is allowed, hence weights_only=False.
+        return torch.load(blob, weights_only=False)
+
+    def _serve(self) -> None:
+        try:
+            self._server.serve_forever()
+        except Exception as e:  # noqa: BLE001
+            logger.exception(f"checkpoint server crashed: {e}")

@@ -33,10 +33,13 @@ class DistributedSampler(data.distributed.DistributedSampler):
             rank / num_replicas: local rank and size inside the group (default: the
                 default process group's)
         """
-        if rank is None:
-            rank = dist.get_rank()
-        if num_replicas is None:
-            num_replicas = dist.get_world_size()
-        self.global_rank: int = rank + num_replicas * replica_group
-        self.global_world_size: int = num_replicas * num_replica_groups
-        super().__init__(dataset, rank=self.global_rank, num_replicas=self.global_world_size, **kwargs)  # type: ignore[arg-type]
+        group_size = dist.get_world_size() if num_replicas is None else num_replicas
+        local_rank = dist.get_rank() if rank is None else rank
+        if not 0 <= replica_group < num_replica_groups:
+            raise ValueError(f"replica_group {replica_group} outside [0, {num_replica_groups})")
+        if not 0 <= local_rank < group_size:
+            raise ValueError(f"rank {local_rank} outside [0, {group_size})")
+        # groups are laid out one after the other: group g owns global ranks [g * size, (g + 1) * size)
+        self.global_world_size: int = num_replica_groups * group_size
+        self.global_rank: int = replica_group * group_size + local_rank
+        super().__init__(dataset, num_replicas=self.global_world_size, rank=self.global_rank, **kwargs)  # type: ignore[arg-type]
