@@ -272,3 +272,45 @@ def test_checkpoint_gate_counts_readers_and_close_waits_for_them():
     with pytest.raises(TimeoutError):
         with gate.reading(timedelta(seconds=0.05)):
             pass
+
+
+def test_optimizer_wrapper_is_a_proxy_that_lr_schedulers_accept():
+    """A scheduler built on the wrapper changes the wrapped optimizer's learning rate, and its
+    re-binding of ``step`` neither bypasses the commit vote nor recurses."""
+    manager = create_autospec(Manager)
+    manager.should_commit.return_value = True
+    layer = nn.Linear(2, 2)
+    base = torch.optim.SGD(layer.parameters(), lr=1.0)
+    optim = OptimizerWrapper(manager, base)
+    assert isinstance(optim, torch.optim.Optimizer)
+    scheduler = torch.optim.lr_scheduler.StepLR(optim, step_size=1, gamma=0.5)
+    optim.zero_grad()
+    layer(torch.ones(2)).sum().backward()
+    before = layer.weight.detach().clone()
+    optim.step()
+    scheduler.step()
+    assert manager.should_commit.call_count == 1
+    assert not torch.equal(layer.weight, before)
+    assert base.param_groups[0]["lr"] == 0.5 and optim.param_groups is base.param_groups
+    optim.defaults["marker"] = 1  # attributes that are not the wrapper's own live on the wrapped optimizer
+    assert base.defaults["marker"] == 1
+
+    manager.should_commit.return_value = False
+    before = layer.weight.detach().clone()
+    optim.step()
+    assert torch.equal(layer.weight, before)
+
+
+def test_pure_ddp_remove_hooks_and_sampler_bounds():
+    manager = create_autospec(Manager)
+    model = PureDistributedDataParallel(manager, nn.Linear(3, 1))
+    model(torch.ones(3)).sum().backward()
+    assert manager.allreduce.call_count == 2
+    model.remove_hooks()
+    model(torch.ones(3)).sum().backward()
+    assert manager.allreduce.call_count == 2
+
+    with pytest.raises(ValueError):
+        DistributedSampler(list(range(8)), replica_group=2, num_replica_groups=2, rank=0, num_replicas=2)
+    with pytest.raises(ValueError):
+        DistributedSampler(list(range(8)), replica_group=0, num_replica_groups=2, rank=2, num_replicas=2)

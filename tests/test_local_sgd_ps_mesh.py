@@ -4,6 +4,7 @@ local_sgd_test.py, parameter_server_test.py and device_mesh_test.py."""
 
 import io
 import os
+import time
 from datetime import timedelta
 from unittest.mock import Mock, create_autospec
 
@@ -164,6 +165,11 @@ def test_parameter_server_round_trip():
         pg.broadcast_one(data, 1).wait()
         pg.broadcast_one(data, 0).wait()
         assert torch.equal(data, torch.full((2, 3), 35.0))
+        # the session leaves the server's table when its forward() has returned
+        deadline = time.monotonic() + 5
+        while ps.open_sessions() and time.monotonic() < deadline:
+            time.sleep(0.01)
+        assert ps.open_sessions() == 0
     finally:
         ps.shutdown()
 
