@@ -456,3 +456,15 @@ def test_wire_codec_round_trips_random_messages():
 
     member_round_trip()
     response_round_trip()
+
+
+def test_extension_module_alias_has_the_reference_names():
+    """``torchft_b200.torchft`` offers what code written for the reference imports from ``torchft.torchft``."""
+    import torchft_b200 as torchft
+    from torchft_b200 import _control
+    from torchft_b200.torchft import Lighthouse, Manager, ManagerClient, QuorumResult
+
+    assert Lighthouse is _control.Lighthouse and Manager is _control.Manager
+    assert ManagerClient is _control.ManagerClient and QuorumResult is _control.QuorumResult
+    for name in ("DistributedDataParallel", "DistributedSampler", "Manager", "Optimizer", "ProcessGroupBabyNCCL", "ProcessGroupGloo"):
+        assert getattr(torchft, name) is not None
