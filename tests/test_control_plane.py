@@ -56,23 +56,38 @@ def test_lighthouse_heartbeat_and_quorum_e2e():
 
 
 def test_lighthouse_quorum_id_stable_until_membership_changes():
-    lh = make_lighthouse(join_timeout_ms=1)
+    # a is usually served alone (fast quorum) just before b asks.  b is then a minority of the
+    # heartbeating replicas and gets its quorum when a's heartbeat has aged out, so the expiry is
+    # short here and b keeps heartbeating while it waits, as a manager does.
+    lh = make_lighthouse(join_timeout_ms=1, heartbeat_timeout_ms=1000)
+    stop = threading.Event()
+
+    def keep_b_alive():
+        beat = C.LighthouseClient(lh.address(), 5 * SEC)
+        while not stop.is_set():
+            beat.heartbeat("b")
+            stop.wait(0.1)
+
     try:
         a = C.LighthouseClient(lh.address(), 5 * SEC)
         q1 = a.quorum(requester("a", step=1), 5 * SEC)
         q2 = a.quorum(requester("a", step=2), 5 * SEC)
         assert q1["quorum_id"] == q2["quorum_id"]
         b = C.LighthouseClient(lh.address(), 5 * SEC)
-        with ThreadPoolExecutor(2) as ex:
+        with ThreadPoolExecutor(3) as ex:
             fa = ex.submit(a.quorum, requester("a", step=3), 5 * SEC)
             time.sleep(0.02)
-            fb = ex.submit(b.quorum, requester("b", step=0), 5 * SEC)
-            qa, qb = fa.result(), fb.result()
-        # a alone may have been served by a fast quorum before b arrived; then b joins the next quorum
+            ex.submit(keep_b_alive)
+            fb = ex.submit(b.quorum, requester("b", step=0), 10 * SEC)
+            try:
+                qa, qb = fa.result(), fb.result()
+            finally:
+                stop.set()
         ids = {p["replica_id"] for p in qb["participants"]}
         assert "b" in ids
         assert qb["quorum_id"] > q1["quorum_id"]
     finally:
+        stop.set()
         lh.shutdown()
 
 
