@@ -2,7 +2,7 @@
 
 Code written against the reference imports ``Manager``, ``ManagerClient``, ``Lighthouse`` and
 ``QuorumResult`` from ``torchft.torchft`` (interface: the reference's ``torchft/torchft.pyi``);
-with ``import torchft_b200 as torchft`` the same import path resolves here, to the C++ classes of
+replacing the package name in such an import leads here, to the C++ classes of
 ``torchft_b200._control``.
 """
 
