@@ -24,7 +24,7 @@ from torchft_b200.process_group import ProcessGroupGloo, ft_init_device_mesh
 class Tiny(nn.Module):
     def __init__(self):
         super().__init__()
-        self.model = nn.Sequential(nn.Linear(3, 4), nn.ReLU(), nn.Linear(4, 2))
+        self.model = nn.Sequential(nn.Linear(3, 4), nn.Tanh(), nn.Linear(4, 2))  # no dead units: every parameter gets a gradient
 
     def forward(self, x):
         return self.model(x)
