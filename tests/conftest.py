@@ -10,6 +10,17 @@ if str(ROOT) not in sys.path:
 
 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
 
+# Property tests draw the same examples on every run unless asked to explore
+# (HYPOTHESIS_PROFILE=explore, or --hypothesis-seed=N on the command line).
+try:
+    from hypothesis import settings as _hypothesis_settings
+
+    _hypothesis_settings.register_profile("repeatable", derandomize=True, database=None)
+    _hypothesis_settings.register_profile("explore", derandomize=False)
+    _hypothesis_settings.load_profile(os.environ.get("HYPOTHESIS_PROFILE", "repeatable"))
+except ImportError:  # the property tests skip themselves without hypothesis
+    pass
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (B200)")
