@@ -124,6 +124,12 @@ class _Gate(Generic[T]):
             self._step, self._payload, self._open = step, payload, True
             self._cond.notify_all()
 
+    def reopen(self, step: int) -> None:
+        """Opens for ``step`` with the payload of the last ``open``."""
+        with self._cond:
+            self._step, self._open = step, True
+            self._cond.notify_all()
+
     def close(self) -> None:
         with self._cond:
             self._open = False
@@ -224,7 +230,7 @@ class CheckpointServer(CheckpointTransport[T]):
     # ---- HTTP specifics
     def allow_checkpoint(self, step: int) -> None:
         """Re-opens the gate for ``step`` with the state dict given to the last ``send_checkpoint``."""
-        self._gate.open(step, self._gate._payload)  # noqa: SLF001
+        self._gate.reopen(step)
 
     def address(self) -> str:
         """``http://<host>:<port>/checkpoint/`` -- append the step to fetch."""
