@@ -35,9 +35,42 @@ def _say(obj) -> None:
 
 
 def run(args) -> None:
+    """Runs the arm and keeps every rank's traceback: a failing rank prints it with its rank number
+    before the launcher tears the other ranks down, so the cause of a non-zero exit is on record."""
+    try:
+        _run(args)
+    except BaseException:
+        import traceback
+
+        sys.stderr.write(f"[reference arm] rank {os.environ.get('RANK', '0')} failed:\n{traceback.format_exc()}\n")
+        sys.stderr.flush()
+        raise
+
+
+def _one_gpu_per_process() -> int:
+    """Shows this process only its own GPU, as ``cuda:0``.
+
+    This is how the reference is launched (its README starts every replica group with its own
+    ``CUDA_VISIBLE_DEVICES``), and its recovery path depends on it: ``CheckpointServer`` sends
+    ``torch.save`` of CUDA tensors and the receiver calls ``torch.load`` without ``map_location``
+    (torchft/checkpointing.py:187-203), which rebuilds every tensor on the device index it was
+    saved from.  With all GPUs visible, every healing replica therefore first materialises the whole
+    state on the sender's GPU 0 and keeps it there until its first ``should_commit``; with seven
+    healers that is 7 x 16 GB on the GPU that also holds replica 0's parameters, gradients and
+    cached activation memory, and a healer runs out of memory.  Must run before CUDA is initialised.
+    """
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    visible = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+    chosen = visible[local_rank] if visible else str(local_rank)
+    os.environ["CUDA_VISIBLE_DEVICES"] = chosen
+    return int(chosen) if chosen.isdigit() else local_rank
+
+
+def _run(args) -> None:
     if args.gpus not in (1, 2, 4, 8):
         _say({"impl": "reference", "unavailable": f"unsupported GPU count {args.gpus}"})
         return
+    physical_gpu = _one_gpu_per_process()  # index for nvidia-smi, which ignores the visible-device list
     # The reference advertises socket.gethostname() in URLs; inside a container that name may
     # not resolve, so make the lookup succeed without touching the reference's files.
     try:
@@ -61,10 +94,13 @@ def run(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    assert torch.cuda.device_count() == 1, "CUDA was initialised before the visible-device list was narrowed"
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # plumbing only (barriers, the lighthouse address, max over ranks); the data plane is the
+        # reference's own ProcessGroupNCCL across the replica groups
+        dist.init_process_group("gloo")
 
     def bcast(obj, src=0):
         if world == 1:
@@ -145,14 +181,20 @@ def run(args) -> None:
     store = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
 
     optimizer_box = {}
+    init_mode = getattr(args, "ref_init", "resume")
+    # With "heal" the replicas that are not the primary fetch the whole state over HTTP at step 0, one
+    # after the other under the server's lock (torchft/checkpointing.py:139-170): budget for world - 1
+    # serial transfers of 16 GB each.
+    budget = timedelta(seconds=300 if init_mode == "resume" else 1800)
     pg = torchft.process_group.ProcessGroupNCCL()
     manager = torchft.Manager(
         pg=pg,
         load_state_dict=lambda sd: (model.load_state_dict(sd["model"]), optimizer_box["o"].load_state_dict(sd["optim"])),
         state_dict=lambda: {"model": model.state_dict(), "optim": optimizer_box["o"].state_dict()},
         min_replica_size=world,
-        timeout=timedelta(seconds=300),
-        quorum_timeout=timedelta(seconds=300),
+        timeout=budget,
+        quorum_timeout=budget,
+        connect_timeout=timedelta(seconds=120),
         rank=0,
         world_size=1,
         store_addr="127.0.0.1",
@@ -164,6 +206,12 @@ def run(args) -> None:
     inner = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
     optimizer = torchft.Optimizer(manager, inner)
     optimizer_box["o"] = inner
+    if init_mode == "resume":
+        # Every replica group built the same weights from the same seed above, i.e. each has "loaded the
+        # same checkpoint".  Restoring the manager's own state_dict with it, as the reference asks of
+        # anyone who resumes from a periodic checkpoint (torchft/manager.py:83-84), puts all groups at
+        # the same step > 0, so the first quorum finds nobody behind and no replica heals at step 0.
+        manager.load_state_dict({"step": 1, "batches_committed": world})
 
     total = args.warmup + 2 * args.steps
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -191,7 +239,7 @@ def run(args) -> None:
     for _ in range(args.warmup):
         one_step(True)
     sync_all()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(physical_gpu)
     if rank == 0:
         sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -210,7 +258,7 @@ def run(args) -> None:
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     if world > 1:
-        t = torch.tensor([device_ms, e2e_s], device=device, dtype=torch.float64)
+        t = torch.tensor([device_ms, e2e_s], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         device_ms, e2e_s = float(t[0]), float(t[1])
     tokens_per_step = world * seq
@@ -236,6 +284,10 @@ def run(args) -> None:
             "parallelism": f"torchft DDP {world}x1 (replica groups x 1 GPU), ProcessGroupNCCL; the reference's "
                            "HSDP mesh glue does not run on torch 2.11, so no sharding inside a group",
             "optimizer": "torch.optim.AdamW(fused=True), bf16 parameters and bf16 moments",
+            "init": ("same seed on every replica group + Manager.load_state_dict(step=1): the reference's resume path, "
+                     "no step-0 heal" if init_mode == "resume" else
+                     "step-0 heal: every other replica group fetches the state from group 0 over the reference's HTTP transport"),
+            "devices": "one visible GPU per process (CUDA_VISIBLE_DEVICES), as the reference's README launches it",
             "note": "reference Python sources unmodified; control-plane extension is a C++ stand-in for the "
                     "unbuildable Rust one; model is plain PyTorch (cuBLAS, SDPA)",
         },

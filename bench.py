@@ -52,6 +52,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--fused-gather", action="store_true",
                     help="shard every projection matrix by rows and gather it inside its first GEMM of the step "
                          "(all-gather fused GEMM) instead of with separate all-gather kernels")
+    ap.add_argument("--ref-init", default="resume", choices=["resume", "heal"],
+                    help="reference arm only: 'resume' starts every replica group from the same seed and the same "
+                         "manager step (no step-0 heal); 'heal' lets group 0 serve its state over HTTP at step 0")
     return ap.parse_args()
 
 
