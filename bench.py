@@ -192,7 +192,7 @@ def run_ours(args: argparse.Namespace) -> None:
     heap = SymmetricHeap.get(heap_bytes, device)
     shard = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
     client_store = TCPStore("127.0.0.1", store_port, is_master=False, wait_for_workers=False)
-    shard.configure(PrefixStore("shard", client_store), shard_rank, shard_world, f"shard-group-{group}")
+    shard.bind(client_store, shard_rank, shard_world, "shard")  # fixed membership; renewed after a failed step
 
     model = Llama(cfg, device=device)
     model.init_weights(seed=1234)  # identical on every rank, as after the step-0 heal
@@ -219,7 +219,7 @@ def run_ours(args: argparse.Namespace) -> None:
     fused = None
     if args.fused_gather and shard_world > 1:
         fused = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
-        fused.configure(PrefixStore("fused", client_store), shard_rank, shard_world, f"fused-group-{group}")
+        fused.bind(client_store, shard_rank, shard_world, "fused")
     engine = HSDPEngine(
         model, model.units(per_weight=fused is not None), manager=manager, shard_comm=NVLinkShardComm(shard),
         lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,

@@ -191,6 +191,140 @@ def test_absent_peer_times_out_without_hanging():
     _spawn(_peer_absent, 2)
 
 
+def _host_gives_up_first(rank, world, port):
+    """The manager's (host) timeout is far shorter than the device budget: when it fires, the manager
+    aborts the process group and the waiting kernel returns at once with status 3 (aborted)."""
+    import time
+
+    from torch.distributed import TCPStore
+
+    from torchft_b200 import _control
+    from torchft_b200.manager import Manager
+    from torchft_b200.parallel.nvlink import ProcessGroupNVLink
+
+    _control.set_log_enabled(False)
+    store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
+    lighthouse = None
+    if rank == 0:
+        lighthouse = _control.Lighthouse(bind="[::]:0", min_replicas=world, join_timeout_ms=20000, quorum_tick_ms=10)
+        store.set("lighthouse", lighthouse.address())
+    group_store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+    pg = ProcessGroupNVLink(timeout=timedelta(seconds=20))  # device-side budget
+    state = {"w": torch.zeros(4, device="cuda")}
+    manager = Manager(
+        pg=pg, load_state_dict=lambda sd: state.update(sd), state_dict=lambda: dict(state), min_replica_size=world,
+        timeout=timedelta(seconds=1),  # host-side budget
+        quorum_timeout=timedelta(seconds=30), rank=0, world_size=1, store_addr="127.0.0.1",
+        store_port=group_store.port, lighthouse_addr=store.get("lighthouse").decode(), replica_id=f"abort_{rank}_",
+        hostname="127.0.0.1",
+    )
+    # step 1: everybody takes part
+    manager.start_quorum()
+    t = torch.ones(1024, device="cuda")
+    manager.allreduce(t).wait()
+    assert manager.should_commit()
+    assert torch.all(t == 1.0).item()
+    # step 2: rank 1 joins the quorum but stays away from the allreduce (a host-side decision)
+    manager.start_quorum()
+    manager.wait_quorum()
+    if rank == 0:
+        t = torch.ones(1024, device="cuda")
+        t0 = time.time()
+        manager.allreduce(t).wait()  # never raises; completes when the host timeout fired
+        torch.cuda.synchronize()  # the kernel itself is over, too: it saw the abort word
+        elapsed = time.time() - t0
+        assert isinstance(manager.errored(), Exception)
+        assert elapsed < 6.0, f"kernel still waited {elapsed:.1f} s after the host had given up"
+        assert pg.communicator.status() == 3, pg.communicator.status()
+        assert not manager.should_commit()
+        store.set("rank0_done", b"1")
+    else:
+        store.get("rank0_done")  # nothing of rank 1 is in flight while rank 0's wait is cut short
+    manager.shutdown(wait=False)
+    if lighthouse is not None:
+        lighthouse.shutdown()
+    return "ok"
+
+
+def test_manager_timeout_aborts_the_waiting_kernel():
+    _need_gpus(2)
+    _spawn(_host_gives_up_first, 2)
+
+
+def _shard_peer_skips(rank, world, port):
+    """One replica group sharded over two GPUs; in step 2 rank 1 stays away from the shard-group
+    collectives.  Rank 0's bounded wait runs out, the status word turns that into a failed vote for the
+    whole group, every rank renews the shard communicator, and step 3 commits again."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200 import _control
+    from torchft_b200.manager import Manager
+    from torchft_b200.models.llama import Llama, LlamaConfig
+    from torchft_b200.parallel.hsdp import HSDPEngine
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, NVLinkShardComm, ProcessGroupNVLink, SymmetricHeap
+
+    _control.set_log_enabled(False)
+    store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
+    lighthouse = None
+    if rank == 0:
+        lighthouse = _control.Lighthouse(bind="[::]:0", min_replicas=1, join_timeout_ms=20000, quorum_tick_ms=10)
+        store.set("lighthouse", lighthouse.address())
+    cfg = LlamaConfig.tiny()
+    heap = SymmetricHeap.get(512 << 20)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=1))
+    comm.bind(PrefixStore("grp", store), rank, world, "shard")
+    shard = NVLinkShardComm(comm)
+    model = Llama(cfg, device="cuda")
+    model.init_weights(seed=3)
+    box = {}
+    manager = Manager(
+        pg=ProcessGroupNVLink(timeout=timedelta(seconds=10), heap=heap, staging_bytes=16 << 20),
+        load_state_dict=lambda sd: box["e"].load_state_dict(sd), state_dict=lambda: box["e"].state_dict(),
+        min_replica_size=1, timeout=timedelta(seconds=30), quorum_timeout=timedelta(seconds=30),
+        rank=rank, world_size=world, store_addr="127.0.0.1", store_port=port,
+        lighthouse_addr=store.get("lighthouse").decode(), replica_id="sharded_", hostname="127.0.0.1",
+    )
+    engine = HSDPEngine(model, model.units(), manager=manager, shard_comm=shard, lr=1e-3, alloc=heap.alloc)
+    box["e"] = engine
+    gen = torch.Generator().manual_seed(11 + rank)
+    tokens = torch.randint(cfg.vocab_size, (1, 256), generator=gen).cuda()
+    targets = torch.randint(cfg.vocab_size, (1, 256), generator=gen).cuda()
+
+    engine.train_step(tokens, targets)
+    assert manager.current_step() == 1
+    engine.wait_optimizer()
+    before = engine.flat_param.clone()
+    real_rs, real_ag = shard.reduce_scatter_, shard.all_gather_
+    if rank == 1:
+        shard.reduce_scatter_ = lambda full, n: None  # stays away, on the host
+        shard.all_gather_ = lambda full, n: None
+    engine.train_step(tokens, targets)
+    shard.reduce_scatter_, shard.all_gather_ = real_rs, real_ag
+    assert manager.current_step() == 1, "a step with partial gradients must not commit"
+    assert comm._generation == 1 and comm.status() == 0
+    # the optimizer did not run: the owned parameter slices are what they were
+    own = slice(0, 0)
+    for u in engine.units:
+        n = u.numel // world
+        own = slice(u.offset + rank * n, u.offset + (rank + 1) * n)
+        assert torch.equal(engine.flat_param[own], before[own])
+    loss = engine.train_step(tokens, targets)
+    assert manager.current_step() == 2
+    assert torch.isfinite(loss).item()
+    store.set(f"done/{rank}", b"1")
+    for r in range(world):
+        store.get(f"done/{r}")
+    manager.shutdown(wait=False)
+    if lighthouse is not None:
+        lighthouse.shutdown()
+    return "ok"
+
+
+def test_shard_peer_missing_fails_the_vote_and_the_group_recovers():
+    _need_gpus(2)
+    _spawn(_shard_peer_skips, 2)
+
+
 def _hsdp_shards(rank, world, port):
     """One replica group sharded over `world` GPUs must match one GPU fed the concatenated batch."""
     from torch.distributed import PrefixStore, TCPStore

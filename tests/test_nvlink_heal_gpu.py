@@ -53,3 +53,23 @@ def test_loopback_pull_gate_and_lease():
             t.recv_checkpoint(0, t.metadata(), 7, timedelta(seconds=0.3))
     finally:
         t.shutdown()
+
+
+def test_http_checkpoint_is_ordered_after_kernels_still_queued():
+    """The HTTP transport copies on a stream of its own; the copy must still see the values that
+    kernels queued BEFORE send_checkpoint produce (here: a long spin followed by a fill)."""
+    from torchft_b200.checkpointing import CheckpointServer
+
+    param = torch.zeros(1 << 20, device="cuda")
+    server = CheckpointServer(timeout=timedelta(seconds=30))
+    try:
+        torch.cuda._sleep(2_000_000_000)  # about a second of GPU time ahead of the write
+        param.fill_(7.0)
+        server.send_checkpoint([1], 3, {"user": {"p": param}, "torchft": {"step": 3, "batches_committed": 3}},
+                               timedelta(seconds=30))
+        got = server.recv_checkpoint(0, server.metadata(), 3, timedelta(seconds=30))
+        server.disallow_checkpoint()
+        assert got["user"]["p"].device.type == "cpu"
+        assert bool((got["user"]["p"] == 7.0).all())
+    finally:
+        server.shutdown(wait=False)

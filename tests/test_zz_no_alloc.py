@@ -4,8 +4,9 @@ Some users of the kernel library cannot allocate device memory at the point wher
 need the kernel (they sit inside an allocator callback, or only own raw pointers and a
 stream), so ``tft_rmsnorm_bwd_noalloc`` keeps its scratch inside the library.  This test
 loads the library on its own, calls that symbol twice in a row and checks both results
-against the regular entry point, which gets its scratch from the caller.  It is collected
-last so a failure here never hides the result of another test.
+against the regular entry point, which gets its scratch from the caller, and against the
+same formulas written in fp32 PyTorch.  It is collected last so a failure here never hides the
+result of another test.
 """
 
 import ctypes
@@ -63,6 +64,13 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         # the two entry points split the rows over a different number of blocks, so the
         # weight gradient is summed in a different order
         assert _rel(dw, dw_ref) < 2e-2, f"call {call}: dw differs by {_rel(dw, dw_ref)}"
+        # and both against plain fp32 PyTorch: y = x * rstd * w, differentiated by autograd
+        xf = x.float().requires_grad_(True)
+        wf = w.float().requires_grad_(True)
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        y.backward(dy.float())
+        assert _rel(dx, xf.grad + dres.float()) < 2e-2, f"call {call}: dx vs fp32 {_rel(dx, xf.grad + dres.float())}"
+        assert _rel(dw, wf.grad) < 2e-2, f"call {call}: dw vs fp32 {_rel(dw, wf.grad)}"
 
 
 def test_noalloc_rejects_oversized_rows():

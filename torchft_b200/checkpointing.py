@@ -41,8 +41,39 @@ T = TypeVar("T")
 _URL_PREFIX = "/checkpoint/"
 
 
-def _compact(state: object) -> object:
+def _cuda_devices(state: object) -> List[torch.device]:
+    """The CUDA devices that hold tensors of ``state``."""
+    from torch.utils._pytree import tree_leaves
+
+    found: Dict[torch.device, None] = {}
+    for leaf in tree_leaves(state):
+        if isinstance(leaf, torch.Tensor) and leaf.device.type == "cuda":
+            found.setdefault(leaf.device, None)
+    return list(found)
+
+
+def _record_ready(state: object) -> Dict[torch.device, "torch.cuda.Event"]:
+    """One event per CUDA device of ``state``, recorded on the caller's current stream there.
+
+    Everything queued so far on that stream that writes the state -- the previous optimizer step, a
+    recovery copy -- precedes the event, so a copy that waits for it reads final values.  The
+    ``Manager`` calls this from its quorum thread, whose current stream is the device's default
+    stream: training that runs on the default stream (or that joins its side streams back into it
+    before the step ends, as ``HSDPEngine.state_dict`` does) is covered.
+    """
+    ready: Dict[torch.device, "torch.cuda.Event"] = {}
+    for device in _cuda_devices(state):
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(device))
+        ready[device] = event
+    return ready
+
+
+def _compact(state: object, ready: Optional[Dict[torch.device, "torch.cuda.Event"]] = None) -> object:
     """Tensors of a state dict as stand-alone CPU tensors.
+
+    ``ready`` maps a CUDA device to an event that the copies from that device wait for (see
+    ``_record_ready``); without it the copies are ordered after nothing.
 
     ``torch.save`` writes the whole storage behind every tensor and refuses storages that are
     viewed under two dtypes.  State that lives as views of one large arena (a symmetric heap, a
@@ -63,6 +94,8 @@ def _compact(state: object) -> object:
             stream = side.get(t.device)
             if stream is None:
                 stream = side[t.device] = torch.cuda.Stream(device=t.device)
+                if ready is not None and t.device in ready:
+                    stream.wait_event(ready[t.device])
             with torch.cuda.device(t.device), torch.cuda.stream(stream):
                 return t.to("cpu")
         if t.device.type != "cpu":
@@ -102,6 +135,10 @@ def _timed_acquire(lock: threading.Lock, timeout: timedelta) -> Generator[None, 
         yield
     finally:
         lock.release()
+
+
+class _Served(tuple):
+    """``(state dict, events that mark it final)`` as kept behind the gate."""
 
 
 class _Gate(Generic[T]):
@@ -175,7 +212,8 @@ def _checkpoint_handler(gate: "_Gate[object]", timeout: timedelta) -> Type[BaseH
                         self.wfile.write(f"invalid checkpoint requested, serving {step} but got {self.path}".encode())
                         return
                     self._head(200, "application/octet-stream")
-                    torch.save(_compact(state), self.wfile)
+                    payload, ready = state if isinstance(state, _Served) else (state, None)
+                    torch.save(_compact(payload, ready), self.wfile)
             except Exception as e:  # noqa: BLE001 - reported to the client
                 logger.exception(f"exception while serving checkpoint: {e}")
                 try:
@@ -207,8 +245,11 @@ class CheckpointServer(CheckpointTransport[T]):
         return self.address()
 
     def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
-        # Nothing is pushed: the state dict is served by reference while the gate is open.
-        self._gate.open(step, state_dict)
+        # Nothing is pushed: the state dict is served by reference while the gate is open.  The serving
+        # thread copies from a stream of its own, which by itself is ordered after nothing: the events
+        # recorded here, on the caller's streams, are what puts those copies after the kernels that
+        # still write the state (the reference gets that order from torch.save running on the default stream).
+        self._gate.open(step, _Served((state_dict, _record_ready(state_dict))))  # type: ignore[arg-type]
 
     def disallow_checkpoint(self) -> None:
         self._gate.close()

@@ -4,7 +4,9 @@
 // All kernels are bandwidth bound: every tensor is read once and written once, with
 // 16-byte vector accesses, and row statistics stay in registers / shared memory.
 #include "common.cuh"
+#include "tft_noalloc.h"
 
+#include <atomic>
 #include <cstdio>
 
 namespace tft {
@@ -318,6 +320,8 @@ TFT_API int tft_rope(void* x, const void* cs, const int* positions, int tokens, 
 //     race on it.  Issue them on one stream or order them yourself.
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress).  Make that first call outside of any stream capture.
+//   * The lookup is for the current device, which therefore has to be the device of `stream`;
+//     a stream of another device is refused (-11).
 //   * No cudaMalloc, cudaFree or allocating library routine is called, ever.
 namespace tft {
 
@@ -330,20 +334,31 @@ static __device__ __align__(256) float g_noalloc_scratch[kNoAllocParts * kNoAllo
 // Device address of g_noalloc_scratch per device ordinal.  In host code the symbol's name
 // is only a host-side stand-in, so the address is resolved through the runtime, once per
 // device, with that device current.
-static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+// Atomic because any host thread may make the first call on a device; racing threads store the same
+// address, so whichever store lands last changes nothing.
+static std::atomic<float*> g_noalloc_ptr[kNoAllocMaxDevices];
 
-static int noalloc_scratch(float** out) {
+static int noalloc_scratch(float** out, cudaStream_t stream) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kNoAllocMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
-  if (g_noalloc_ptr[dev] == nullptr) {
+  int stream_dev = dev;
+  if (cudaStreamGetDevice(stream, &stream_dev) == cudaSuccess && stream_dev != dev) {
+    std::fprintf(stderr, "tft_rmsnorm_bwd_noalloc: stream belongs to device %d but device %d is current\n",
+                 stream_dev, dev);
+    return -11;
+  }
+  cudaGetLastError();  // a failed query must not linger as this thread's last error
+  float* cached = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return static_cast<int>(e);
-    g_noalloc_ptr[dev] = static_cast<float*>(p);
+    cached = static_cast<float*>(p);
+    g_noalloc_ptr[dev].store(cached, std::memory_order_release);
   }
-  *out = g_noalloc_ptr[dev];
+  *out = cached;
   return 0;
 }
 
@@ -368,7 +383,7 @@ TFT_API int tft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w
   const int vpt = norm_config(dim, &threads);
   if (!vpt || rows <= 0) return static_cast<int>(cudaErrorInvalidValue);
   float* scratch = nullptr;
-  const int rc = noalloc_scratch(&scratch);
+  const int rc = noalloc_scratch(&scratch, stream);
   if (rc != 0) return rc;
   const int parts = rows < kNoAllocParts ? rows : kNoAllocParts;
   auto DY = static_cast<const __nv_bfloat16*>(dy);

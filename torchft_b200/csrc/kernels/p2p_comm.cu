@@ -213,7 +213,8 @@ __global__ void barrier_kernel(Comm c) {
 // stores it (rounded to the weight type) into chunk r of every replica's gradient buffer.
 // Then all blocks of all replicas meet: the last block of a rank runs the end hand-shake with the
 // peers and releases the rank's other blocks through `phase_flag` (every block is resident: the
-// grid is at most one block per SM).
+// grid is at most one block per SM and goes out as a cooperative launch; nothing else should be
+// queued to run beside it, since a cooperative grid waits until all of its blocks fit).
 // Phase 2 (local): Nesterov momentum and the new global weights for the WHOLE buffer,
 //     b = first ? g : mu * buf + g;   step = nesterov ? g + mu * b : b;   w = global - lr * step
 // written to `global_out` / `mom_out`, which the host swaps in only if the step commits.
@@ -553,11 +554,18 @@ TFT_API int tft_diloco_outer(void* const* heaps, int rank, int world, unsigned e
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  // all blocks wait for one another between the phases: never more blocks than SMs
+  // All blocks wait for one another between the phases, so all of them must be resident at the same
+  // time.  A cooperative launch is what guarantees that: the grid starts only once every block has a
+  // slot (it queues behind kernels that hold SMs instead of starting partially and spinning), and a
+  // grid that can never fit is refused with an error.  Never more blocks than SMs.
+  const void* fn = is_bf16 ? reinterpret_cast<const void*>(&diloco_outer_kernel<__nv_bfloat16>)
+                           : reinterpret_cast<const void*>(&diloco_outer_kernel<float>);
+  int per_sm = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, 512, 0);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (per_sm < 1) return static_cast<int>(cudaErrorCooperativeLaunchTooLarge);
   int grid = grid_for(a.nvec, max_blocks < sm_count ? max_blocks : sm_count);
-  if (is_bf16)
-    diloco_outer_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(c, a);
-  else
-    diloco_outer_kernel<float><<<grid, 512, 0, stream>>>(c, a);
-  return static_cast<int>(cudaGetLastError());
+  void* params[] = {&c, &a};
+  e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(512), params, 0, stream);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }

@@ -56,9 +56,14 @@ __device__ __forceinline__ uint32_t flag_value(uint32_t epoch, uint32_t seq, uin
 // Threads 0..world-1 of the calling block poll; the result is block-uniform.
 // contrib_mask receives one bit per peer.  Returns false on time-out or abort.
 __device__ inline bool wait_pad(const Comm& c, int pad, uint32_t seq, uint32_t* contrib_mask, int* smem_flag) {
-  if (threadIdx.x == 0) { smem_flag[0] = 1; smem_flag[1] = 0; }
+  if (threadIdx.x == 0) {
+    // A communicator whose status word is set has already lost a peer in this membership: later
+    // collectives fail at once instead of sitting out the budget again (configure clears the word).
+    smem_flag[0] = (c.status && *reinterpret_cast<volatile int*>(c.status) != 0) ? 0 : 1;
+    smem_flag[1] = 0;
+  }
   __syncthreads();
-  if (threadIdx.x < c.world) {
+  if (smem_flag[0] != 0 && threadIdx.x < c.world) {
     const uint32_t* slot = reinterpret_cast<const uint32_t*>(c.heap[c.rank]) + c.pad_base + pad + threadIdx.x;
     const uint32_t want = flag_value(c.epoch, seq, 0) >> 1;
     const unsigned long long t0 = now_ns();

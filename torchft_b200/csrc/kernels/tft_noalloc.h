@@ -19,23 +19,35 @@
 //     Calls that overlap on the GPU race; keep them on one stream or order them.
 //   * First call: the first call on each device resolves the array's device address; make
 //     it before any stream capture begins.
+//   * Device: the array is per GPU and is looked up for the CURRENT device, so the current
+//     device must be the one `stream` belongs to (cudaSetDevice first, as for any launch).  A
+//     stream of another device is rejected with return code -11.
+//   * Threads: any host thread may call; the per-device address cache is atomic, and two
+//     threads that race on the first call both store the same value.
 //   * No cudaMalloc, cudaFree or allocating library call is made.
 #pragma once
 
 #include <cuda_runtime.h>
+
+#if defined(__GNUC__)
+#define TFT_NOALLOC_API __attribute__((visibility("default")))
+#else
+#define TFT_NOALLOC_API
+#endif
 
 #ifdef __cplusplus
 extern "C" {
 #endif
 
 // Largest supported row width.
-int tft_rmsnorm_bwd_noalloc_max_dim(void);
+TFT_NOALLOC_API int tft_rmsnorm_bwd_noalloc_max_dim(void);
 
 // dy, x, dres (optional), dx: [rows, dim] bf16;  w, dw: [dim] bf16;  rstd: [rows] fp32.
 //   dx = d loss / d x of y = x * rstd * w  (+ dres if given)
 //   dw = sum over rows of dy * x * rstd    (added to dw when accumulate != 0)
-// Returns 0 on success, -10 if dim is too large, another non-zero code on failure.
-int tft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+// Returns 0 on success, -10 if dim is too large, -11 if `stream` is not a stream of the current
+// device, another non-zero code on failure.
+TFT_NOALLOC_API int tft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                             void* dx, void* dw, int rows, int dim, int accumulate, cudaStream_t stream);
 
 #ifdef __cplusplus

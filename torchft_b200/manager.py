@@ -276,6 +276,23 @@ class Manager:
         """Marks the current step as failed; it will not commit and the group reconfigures."""
         self._errored = e
 
+    def _abort_process_group(self) -> None:
+        """Ends what the process group still has in flight, where the group can do that.
+
+        Called once the host has given up on a collective (its future failed or ran into the
+        manager's timeout): a kernel of the NVLink group that still waits for a peer returns within
+        milliseconds instead of sitting out its own, longer, device-side budget, and an NCCL
+        communicator is torn down as the reference does on reconfiguration
+        (torchft/process_group.py:265-268).  The step is lost either way and the next quorum asks
+        for a reconfiguration, which re-arms the group.
+        """
+        abort = getattr(self._pg, "abort", None)
+        if callable(abort):
+            try:
+                abort()
+            except Exception as e:  # noqa: BLE001 - best effort; the step is discarded anyway
+                self._logger.warn(f"abort of the process group failed: {e}")
+
     def errored(self) -> Optional[Exception]:
         return self._errored
 
@@ -290,6 +307,7 @@ class Manager:
             except Exception as e:  # noqa: BLE001 - recorded, the step is discarded
                 self._logger.exception(f"got exception in future -- skipping remaining: {e}")
                 self.report_error(e)
+                self._abort_process_group()
                 return default
 
         guarded = future_timeout(fut, timeout if timeout is not None else self._timeout).then(absorb)

@@ -64,6 +64,14 @@ class ShardComm:
     def all_gather_(self, full: torch.Tensor, shard_numel: int) -> None:
         """Every rank's slice r is copied into slice r of every other rank's ``full``."""
 
+    def status_async(self):
+        """``(pinned int32 tensor, event)``: after the event, non-zero means that a collective queued
+        before this call gave up waiting for a peer.  ``None``: this backend raises instead."""
+        return None
+
+    def renew(self) -> None:
+        """Called on every rank of the group after a step that did not commit."""
+
 
 class HSDPEngine:
     def __init__(
@@ -144,6 +152,7 @@ class HSDPEngine:
         for u in self.units:
             self._by_prefix.setdefault(u.name.split("/", 1)[0], []).append(u)
         self._fused_units: List[Unit] = []
+        self._fused_comm = fused_gather_comm if S > 1 else None
         if fused_gather_comm is not None and S > 1:
             for u in self.units:
                 if len(u.params) != 1 or u.params[0].dim() != 2 or not getattr(u.params[0], "linear_weight", False):
@@ -217,10 +226,34 @@ class HSDPEngine:
         """
         for u in reversed(self.units):  # backward order: the last units finished first
             self._sync_unit(u)
+        # The shard-group kernels report a peer that never showed up through a status word, not an
+        # exception: fetch it behind the last collective of each communicator.
+        probes = []
+        if self.comm.world > 1 and self.comm_stream is not None:
+            with torch.cuda.stream(self.comm_stream):
+                probes.append(("shard-group collective", self.comm.status_async()))
+            if self._fused_comm is not None:
+                probes.append(("fused all-gather GEMM", self._fused_comm.status_async()))  # ran on this stream
         for f in self._futures:
             f.wait()
         self._futures = []
+        for what, probe in probes:
+            if probe is None:
+                continue
+            status, event = probe
+            event.synchronize()
+            code = int(status.item())
+            if code != 0:
+                self._shard_failure(TimeoutError(
+                    f"{what}: device-side wait gave up (status {code}); gradients or parameters of this step are partial"))
         torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+
+    def _shard_failure(self, error: Exception) -> None:
+        """A collective inside the replica group failed: the step must not commit anywhere in the group."""
+        if self.manager is not None:
+            self.manager.report_error(error)
+        else:
+            raise error
 
     def optimizer_step(self, grad_scale: float = 1.0) -> None:
         """Fused AdamW on the owned slices (the next step starts by all-gathering them).
@@ -320,6 +353,14 @@ class HSDPEngine:
         grad_scale = 1.0 / self.comm.world  # reduce-scatter sums over the shard group
         if self.manager is None or self.manager.should_commit():
             self.optimizer_step(grad_scale)
+        elif self.comm.world > 1:
+            # The vote is group-wide, so every rank of the group is here: all move to fresh flags and
+            # sequence numbers, whichever of them saw the failure (one side may have given up on a
+            # collective that the other side completed or never started).
+            torch.cuda.synchronize(self.device)
+            self.comm.renew()
+            if self._fused_comm is not None and getattr(self._fused_comm, "_bound", None) is not None:
+                self._fused_comm.renew()
         return loss.detach()
 
     # ------------------------------------------------------------------ state for live recovery

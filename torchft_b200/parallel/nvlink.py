@@ -180,7 +180,14 @@ _WATCHER = _Watcher()
 
 
 class _StreamWork(dist._Work):
-    """Work that ran on a side stream: ``wait`` orders the caller's stream after it."""
+    """Work that ran on a side stream.
+
+    ``wait`` blocks the calling thread until the kernel has finished (at most ``timeout``), raises
+    ``TimeoutError`` if a device-side wait inside it gave up, and orders the caller's current stream
+    after it.  Blocking is what lets a caller that only ever calls ``wait()`` (FSDP2 through
+    ``ManagedProcessGroup``) learn of a failed collective; ``get_future`` reports the same outcome
+    without blocking.
+    """
 
     def __init__(self, event: torch.cuda.Event, fut: Future) -> None:
         super().__init__()
@@ -188,6 +195,13 @@ class _StreamWork(dist._Work):
         self._fut = fut
 
     def wait(self, timeout: Optional[timedelta] = None) -> bool:
+        if timeout is not None:
+            deadline = time.monotonic() + timeout.total_seconds()
+            while not self._fut.done():
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"NVLink collective did not finish within {timeout}")
+                time.sleep(0.0005)
+        self._fut.wait()  # raises what the watcher recorded (device status, CUDA error)
         torch.cuda.current_stream().wait_event(self._event)
         return True
 
@@ -223,26 +237,53 @@ class NVLinkCommunicator:
         self._abort_dev = dev
         self._status_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stream = torch.cuda.Stream(device=self.device)
+        self._bound: Optional[Tuple[Store, str]] = None
+        self._generation = 0
+        self._status_pinned: Optional[torch.Tensor] = None
         self._block_ready: Optional[torch.Tensor] = None  # per-block counters of the fused all-gather GEMM
         self._phase_flag: Optional[torch.Tensor] = None  # phase word of the fused DiLoCo outer step
 
     # ------------------------------------------------------------------ membership
-    def configure(self, store: Store, rank: int, world: int, epoch_key: str) -> None:
+    @staticmethod
+    def epoch_of(epoch_key) -> int:
+        """The 11-bit membership tag (1..2047) that every flag of a membership carries.
+
+        An integer (the quorum id, a generation counter) maps to ``n mod 2047 + 1``, so consecutive
+        memberships always differ and two equal tags are 2047 reconfigurations apart.  A string that
+        ends in ``.../<integer>`` or ``.../<integer>/<rank>`` (the store prefix the ``Manager`` hands
+        to ``configure``: ``host:port/torchft/<quorum_id>/<rank>``) is read as that integer; any other
+        string is hashed, which keeps distinct names apart only with probability 2046/2047.
+        """
+        if isinstance(epoch_key, int):
+            return epoch_key % 2047 + 1
+        parts = [p for p in str(epoch_key).split("/") if p]
+        if "torchft" in parts[:-1]:
+            tail = parts[parts.index("torchft") + 1]
+            if tail.isdigit():
+                return int(tail) % 2047 + 1
+        if parts and parts[-1].isdigit():
+            return int(parts[-1]) % 2047 + 1
+        return (zlib.crc32(str(epoch_key).encode()) % 2047) + 1
+
+    def configure(self, store: Store, rank: int, world: int, epoch_key) -> None:
         """Joins the membership identified by ``store`` (a prefix unique to it).
 
         Exchanges heap handles, maps new peers, clears this communicator's flags and
         synchronises through the store so nobody signals into a header that is about to
-        be cleared.
+        be cleared.  ``epoch_key`` names the membership (see ``epoch_of``); every member must
+        pass the same one.
         """
         if world > MAX_RANKS:
             raise ValueError(f"at most {MAX_RANKS} ranks per NVLink communicator, got {world}")
         lib = _lib_p2p()
-        self._abort_host[0] = 0
         self.rank, self.world = rank, world
-        self.epoch = (zlib.crc32(epoch_key.encode()) & 0x7FF) or 1
+        self.epoch = self.epoch_of(epoch_key)
         self.seq = 0
         with torch.cuda.device(self.device):
-            torch.cuda.synchronize(self.device)  # nothing of the old membership may still run
+            # Nothing of the old membership may still run.  The abort word is cleared only afterwards:
+            # kernels that an abort() was meant to end must still see it while they drain.
+            torch.cuda.synchronize(self.device)
+            self._abort_host[0] = 0
             self._status_dev.zero_()
             _lib.check(lib.tft_p2p_reset_channel(self.heap.ptr, self.channel, _lib.stream_ptr()), "tft_p2p_reset_channel")
             torch.cuda.synchronize(self.device)
@@ -272,6 +313,33 @@ class NVLinkCommunicator:
     def abort(self) -> None:
         """Makes every wait of kernels in flight give up (host-side kill switch)."""
         self._abort_host[0] = 1
+
+    def bind(self, store: Store, rank: int, world: int, name: str) -> None:
+        """For a communicator whose members never change (the shard group of a replica group):
+        configures it as generation 0 of ``name`` and remembers the store, so ``renew`` can move
+        all members to the next generation after a failed step."""
+        self._bound = (store, name)
+        self._generation = 0
+        self.configure(dist.PrefixStore(f"{name}/gen0", store), rank, world, 0)
+
+    def renew(self) -> None:
+        """Next generation of a bound communicator: fresh flags, sequence numbers, status and abort
+        word.  Every member must call it the same number of times (e.g. whenever the group-wide
+        commit vote fails)."""
+        store, name = self._bound
+        self._generation += 1
+        self.configure(dist.PrefixStore(f"{name}/gen{self._generation}", store), self.rank, self.world, self._generation)
+
+    def status_async(self) -> Tuple[torch.Tensor, torch.cuda.Event]:
+        """Queues a copy of the status word to pinned host memory on the current stream.  Returns the
+        host tensor and an event; after ``event.synchronize()`` a non-zero value means that a wait of
+        an earlier collective on this stream gave up."""
+        if self._status_pinned is None:
+            self._status_pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_pinned.copy_(self._status_dev, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(self.device))
+        return self._status_pinned, event
 
     # ------------------------------------------------------------------ launch helpers
     def _head(self):
@@ -585,3 +653,11 @@ class NVLinkShardComm:
 
     def all_gather_(self, full: torch.Tensor, shard_numel: int) -> None:
         self.comm.all_gather_(full)
+
+    def status_async(self):
+        return self.comm.status_async()
+
+    def renew(self) -> None:
+        """After a step that did not commit: all members move to fresh flags (needs ``comm.bind``)."""
+        if self.comm._bound is not None:
+            self.comm.renew()

@@ -448,7 +448,17 @@ class ManagedProcessGroup(ProcessGroupWrapper):
         if self._manager.errored() is not None:
             return _DummyWork(tensors)
         try:
-            work = super().allreduce(tensors, opts)
+            op = opts.reduceOp if hasattr(opts, "reduceOp") else opts
+            if len(tensors) == 1 and op in (ReduceOp.SUM, ReduceOp.AVG):
+                # A replica that is still healing (or a spare) is a member of the group but its data
+                # must not count, and an average is over the participants, not over the members:
+                # both are what allreduce_scaled expresses (the reference hands ``opts`` to the
+                # backend unchanged, so NCCL's AVG divides by the member count there).
+                scale = 1.0 / max(self._manager.num_participants(), 1) if op == ReduceOp.AVG else 1.0
+                work = self._manager._pg.allreduce_scaled(
+                    tensors[0], scale, contribute=self._manager.is_participating())
+            else:
+                work = super().allreduce(tensors, opts)
         except Exception as e:  # noqa: BLE001 - reported, the step is discarded
             self._manager.report_error(e)
             return _DummyWork(tensors)
