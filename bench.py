@@ -52,6 +52,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--fused-gather", action="store_true",
                     help="shard every projection matrix by rows and gather it inside its first GEMM of the step "
                          "(all-gather fused GEMM) instead of with separate all-gather kernels")
+    ap.add_argument("--gather-engine", default="sm", choices=["sm", "copy", "copy-push"],
+                    help="parameter all-gather inside a replica group: one SM kernel per unit, or the copy engines "
+                         "(pull / push) between two barrier kernels")
     ap.add_argument("--ref-init", default="resume", choices=["resume", "heal"],
                     help="reference arm only: 'resume' starts every replica group from the same seed and the same "
                          "manager step (no step-0 heal); 'heal' lets group 0 serve its state over HTTP at step 0")
@@ -221,7 +224,7 @@ def run_ours(args: argparse.Namespace) -> None:
         fused = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
         fused.bind(client_store, shard_rank, shard_world, "fused")
     engine = HSDPEngine(
-        model, model.units(per_weight=fused is not None), manager=manager, shard_comm=NVLinkShardComm(shard),
+        model, model.units(per_weight=fused is not None), manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine),
         lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,
     )
     engine_box["engine"] = engine
@@ -316,7 +319,7 @@ def run_ours(args: argparse.Namespace) -> None:
                 "optimizer": "fused AdamW lr 3e-4 betas (0.9, 0.95) wd 0.1, fp32 moments",
                 "quorum": "lighthouse quorum + should_commit every step",
                 "parameter_gather": ("inside the first GEMM of each projection (all-gather fused GEMM)" if fused is not None
-                                     else "per-unit all-gather kernels overlapped with forward"),
+                                     else f"per-unit all-gather ({args.gather_engine}) overlapped with forward"),
                 "l2_policy": "no flush needed: weights, gradients and activations streamed per step exceed 100 GB (L2 is 126 MB)",
             },
             "clocks": clocks,

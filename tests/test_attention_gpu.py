@@ -27,6 +27,11 @@ def rel(a, b):
     return ((a.float() - b).abs().max() / b.abs().max()).item()
 
 
+def norm_rel(a, b):
+    """Frobenius norm of the error over that of the reference (about 2e-3 for a correct bf16 result)."""
+    return ((a.float() - b).norm() / b.norm()).item()
+
+
 @pytest.mark.parametrize("shape", [(1, 128, 1, 1, 128), (2, 512, 4, 2, 128), (1, 384, 4, 1, 64), (1, 200, 2, 2, 128), (1, 1024, 8, 2, 128)])
 def test_attention_fwd_bwd(shape):
     from torchft_b200.ops import _lib
@@ -39,8 +44,27 @@ def test_attention_fwd_bwd(shape):
     o = attention(q, k, v)
     o.backward(do)
     ro, _, rq, rk, rv = reference(q.detach(), k.detach(), v.detach(), do)
-    assert rel(o, ro) < 2e-2
+    assert rel(o, ro) < 2e-2 and norm_rel(o, ro) < 6e-3
     assert rel(q.grad, rq) < 2e-2 and rel(k.grad, rk) < 2e-2 and rel(v.grad, rv) < 2e-2
+    assert norm_rel(q.grad, rq) < 8e-3 and norm_rel(k.grad, rk) < 8e-3 and norm_rel(v.grad, rv) < 8e-3
+    _lib.check_status("attention")
+
+
+def test_attention_at_the_benchmark_shape():
+    """One sequence of 4096 tokens, 32 query heads over 8 key/value heads, head dimension 128."""
+    from torchft_b200.ops import _lib
+    from torchft_b200.ops.attention import attention
+
+    B, S, Hq, Hkv, D = 1, 4096, 32, 8, 128
+    torch.manual_seed(2)
+    q, k, v = (torch.randn(B, S, h, D, device="cuda").to(torch.bfloat16).requires_grad_() for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+    o = attention(q, k, v)
+    o.backward(do)
+    ro, _, rq, rk, rv = reference(q.detach(), k.detach(), v.detach(), do)
+    assert rel(o, ro) < 2e-2 and norm_rel(o, ro) < 6e-3
+    assert rel(q.grad, rq) < 2e-2 and rel(k.grad, rk) < 2e-2 and rel(v.grad, rv) < 2e-2
+    assert norm_rel(q.grad, rq) < 8e-3 and norm_rel(k.grad, rk) < 8e-3 and norm_rel(v.grad, rv) < 8e-3
     _lib.check_status("attention")
 
 

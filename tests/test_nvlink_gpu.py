@@ -94,6 +94,13 @@ def _collectives(rank, world, port):
     assert (full[sl].float() - ref[sl]).abs().max().item() < 4e-2
     comm.all_gather_(full)
     assert (full.float() - ref).abs().max().item() < 4e-2
+    # the same exchange by the copy engines, pulled and pushed
+    for engine in ("copy", "copy-push"):
+        mine = full[sl].clone()
+        full.zero_()
+        full[sl] = mine
+        comm.all_gather_(full, engine)
+        assert (full.float() - ref).abs().max().item() < 4e-2, engine
     b = heap.alloc(1024, torch.float32)
     b.fill_(float(rank + 1))
     comm.broadcast_(b, world - 1)

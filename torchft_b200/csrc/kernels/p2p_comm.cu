@@ -482,6 +482,35 @@ TFT_API int tft_p2p_all_gather(void* const* heaps, int rank, int world, unsigned
   return static_cast<int>(cudaGetLastError());
 }
 
+// All-gather by the copy engines: a barrier kernel (one block), world - 1 peer copies issued with
+// cudaMemcpyAsync, a second barrier kernel.  No SM moves data, so a GEMM that runs beside it keeps
+// its SMs, its issue slots and its share of the power budget.  `pull` != 0: this rank copies every
+// peer's slice into its own buffer (all of this rank's data is local once its copies are done; the
+// closing barrier only tells the peers that their slice is no longer being read).  `pull` == 0: this
+// rank copies its slice into every peer's buffer (the closing barrier is what makes the received
+// slices final).  Takes TWO sequence numbers: seq and seq + 1.
+TFT_API int tft_p2p_all_gather_ce(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq,
+                                  int timeout_ms, const int* abort_word, int* status, long long off,
+                                  long long slice_bytes, int pull, cudaStream_t stream) {
+  if ((off | slice_bytes) & 15) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  for (int k = 1; k < world; ++k) {
+    const int p = (rank + k) % world;
+    const int owner = pull ? p : rank;          // whose slice moves
+    const int from = pull ? p : rank, to = pull ? rank : p;
+    const size_t at = static_cast<size_t>(off) + static_cast<size_t>(owner) * static_cast<size_t>(slice_bytes);
+    e = cudaMemcpyAsync(c.heap[to] + at, c.heap[from] + at, static_cast<size_t>(slice_bytes),
+                        cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  c.seq = seq + 1;
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  return static_cast<int>(cudaGetLastError());
+}
+
 TFT_API int tft_p2p_broadcast(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
                               const int* abort_word, int* status, long long off, long long bytes, int root,
                               int max_blocks, cudaStream_t stream) {

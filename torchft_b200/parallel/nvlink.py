@@ -61,6 +61,7 @@ def _lib_p2p() -> ctypes.CDLL:
             "tft_p2p_allreduce": head + [L, L, I, F, I, I, P],
             "tft_p2p_reduce_scatter": head + [L, L, I, F, I, P],
             "tft_p2p_all_gather": head + [L, L, I, P],
+            "tft_p2p_all_gather_ce": head + [L, L, I, P],
             "tft_p2p_broadcast": head + [L, L, I, I, P],
             "tft_p2p_barrier": head + [P],
             "tft_ag_gemm_bf16": head + [P, L, P, I, I, I, I, I, P, I, P],
@@ -396,15 +397,32 @@ class NVLinkCommunicator:
         _lib.check(code, "tft_p2p_reduce_scatter")
         _lib.count_launch()
 
-    def all_gather_(self, full: torch.Tensor) -> None:
-        """Slice r of rank r is pushed into slice r of every peer's ``full``."""
+    def all_gather_(self, full: torch.Tensor, engine: str = "sm") -> None:
+        """Every rank ends with all ``world`` slices of ``full``; on entry slice r of rank r is valid.
+
+        ``engine="sm"``: one kernel pushes this rank's slice into every peer's buffer.
+        ``engine="copy"`` / ``"copy-push"``: the GPU's copy engines move the slices (pulled from, or
+        pushed to, the peers) between two one-block barrier kernels, which leaves every SM to whatever
+        computes at the same time.
+        """
         if self.world == 1:
             return
         slice_bytes = full.numel() * full.element_size() // self.world
         assert slice_bytes % 16 == 0
-        code = _lib_p2p().tft_p2p_all_gather(*self._head(), self._offset(full), slice_bytes, self.max_blocks, _lib.stream_ptr())
-        _lib.check(code, "tft_p2p_all_gather")
-        _lib.count_launch()
+        if engine == "sm":
+            code = _lib_p2p().tft_p2p_all_gather(*self._head(), self._offset(full), slice_bytes, self.max_blocks,
+                                                 _lib.stream_ptr())
+            _lib.check(code, "tft_p2p_all_gather")
+            _lib.count_launch()
+            return
+        if engine not in ("copy", "copy-push"):
+            raise ValueError(f"unknown all-gather engine {engine!r}")
+        head = self._head()
+        self.seq += 1  # the closing barrier's sequence number
+        code = _lib_p2p().tft_p2p_all_gather_ce(*head, self._offset(full), slice_bytes, 1 if engine == "copy" else 0,
+                                                _lib.stream_ptr())
+        _lib.check(code, "tft_p2p_all_gather_ce")
+        _lib.count_launch(2)
 
     def all_gather_linear(self, x: torch.Tensor, w_full: torch.Tensor, out: Optional[torch.Tensor] = None,
                           copy_ctas: int = 16) -> torch.Tensor:
@@ -637,8 +655,10 @@ class ProcessGroupNVLink(ProcessGroup):
 class NVLinkShardComm:
     """Shard-dimension collectives of the HSDP engine over a fixed replica-group communicator."""
 
-    def __init__(self, comm: NVLinkCommunicator) -> None:
+    def __init__(self, comm: NVLinkCommunicator, gather_engine: str = "sm") -> None:
+        """``gather_engine``: how parameter slices are all-gathered (see ``NVLinkCommunicator.all_gather_``)."""
         self.comm = comm
+        self.gather_engine = gather_engine
 
     @property
     def rank(self) -> int:
@@ -652,7 +672,7 @@ class NVLinkShardComm:
         self.comm.reduce_scatter_(full, 1.0)
 
     def all_gather_(self, full: torch.Tensor, shard_numel: int) -> None:
-        self.comm.all_gather_(full)
+        self.comm.all_gather_(full, self.gather_engine)
 
     def status_async(self):
         return self.comm.status_async()
@@ -661,3 +681,7 @@ class NVLinkShardComm:
         """After a step that did not commit: all members move to fresh flags (needs ``comm.bind``)."""
         if self.comm._bound is not None:
             self.comm.renew()
+        else:
+            # Not bound to a store: the members cannot meet again, but the sticky status must not fail
+            # every later step.  Flags of the lost step can then still be pending on a peer; use bind().
+            self.comm._status_dev.zero_()
