@@ -225,13 +225,15 @@ def _host_gives_up_first(rank, world, port):
         store_port=group_store.port, lighthouse_addr=store.get("lighthouse").decode(), replica_id=f"abort_{rank}_",
         hostname="127.0.0.1",
     )
-    # step 1: everybody takes part
+    # step 1 (quorum, first configuration, initial weight sync) gets a generous host budget
+    manager._timeout = timedelta(seconds=30)
     manager.start_quorum()
     t = torch.ones(1024, device="cuda")
     manager.allreduce(t).wait()
     assert manager.should_commit()
     assert torch.all(t == 1.0).item()
     # step 2: rank 1 joins the quorum but stays away from the allreduce (a host-side decision)
+    manager._timeout = timedelta(seconds=1)
     manager.start_quorum()
     manager.wait_quorum()
     if rank == 0:

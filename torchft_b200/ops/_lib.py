@@ -24,6 +24,7 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 # name -> argument types (return type is always int: a cudaError_t, 0 on success)
 _PROTOTYPES = {
     "tft_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
+    "tft_gemm2_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
     "tft_rmsnorm_bwd_parts": [I],
     "tft_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
     "tft_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
