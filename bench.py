@@ -52,6 +52,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--fused-gather", action="store_true",
                     help="shard every projection matrix by rows and gather it inside its first GEMM of the step "
                          "(all-gather fused GEMM) instead of with separate all-gather kernels")
+    ap.add_argument("--fused-rs", action="store_true",
+                    help="shard every projection matrix by rows and reduce-scatter its gradient inside the "
+                         "weight-gradient GEMM (no reduce-scatter kernel for those matrices)")
     ap.add_argument("--gather-engine", default="sm", choices=["sm", "copy", "copy-push"],
                     help="parameter all-gather inside a replica group: one SM kernel per unit, or the copy engines "
                          "(pull / push) between two barrier kernels")
@@ -223,8 +226,12 @@ def run_ours(args: argparse.Namespace) -> None:
     if args.fused_gather and shard_world > 1:
         fused = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
         fused.bind(client_store, shard_rank, shard_world, "fused")
+    fused_rs = None
+    if args.fused_rs and shard_world > 1:
+        fused_rs = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
+        fused_rs.bind(client_store, shard_rank, shard_world, "fused_rs")
     engine = HSDPEngine(
-        model, model.units(per_weight=fused is not None), manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine),
+        model, model.units(per_weight=fused is not None or fused_rs is not None), fused_rs_comm=fused_rs, manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine),
         lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,
     )
     engine_box["engine"] = engine
@@ -320,6 +327,8 @@ def run_ours(args: argparse.Namespace) -> None:
                 "quorum": "lighthouse quorum + should_commit every step",
                 "parameter_gather": ("inside the first GEMM of each projection (all-gather fused GEMM)" if fused is not None
                                      else f"per-unit all-gather ({args.gather_engine}) overlapped with forward"),
+                "gradient_reduce_scatter": ("inside the weight-gradient GEMM of every projection matrix" if fused_rs is not None
+                                            else "one kernel per unit after its backward"),
                 "l2_policy": "no flush needed: weights, gradients and activations streamed per step exceed 100 GB (L2 is 126 MB)",
             },
             "clocks": clocks,

@@ -11,7 +11,7 @@ matters, launches each kernel a handful of times and prints CUDA-event timings w
 achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` if present).  Profile one
 kernel of a case with, for example:
 
-    ncu --set full --clock-control none -k regex:gemm_kernel -s 6 -c 1 -o prof \
+    ncu --set full --clock-control none -k regex:gemm2_kernel -s 2 -c 1 -o prof \
         python benchmarks/kernel_cases.py gemm
 """
 
@@ -67,9 +67,11 @@ def case_gemm():
     M = N = K = 8192
     a, b, c = bf16(M, K), bf16(N, K), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     fl = 2.0 * M * N * K
-    report("gemm_kernel<K-major A, K-major B> (forward)", timeit(lambda: gemm(a, b, c)), flops=fl)
-    report("gemm_kernel<K-major A, MN-major B> (dgrad)", timeit(lambda: gemm(a, b, c, b_kmajor=False)), flops=fl)
-    report("gemm_kernel<MN-major A, MN-major B> (wgrad)", timeit(lambda: gemm(a, b, c, a_kmajor=False, b_kmajor=False)), flops=fl)
+    for impl, kernel in (("pair", "gemm2_kernel"), ("single", "gemm_kernel")):
+        report(f"{kernel}<K-major A, K-major B> (forward)", timeit(lambda: gemm(a, b, c, impl=impl)), flops=fl)
+        report(f"{kernel}<K-major A, MN-major B> (dgrad)", timeit(lambda: gemm(a, b, c, b_kmajor=False, impl=impl)), flops=fl)
+        report(f"{kernel}<MN-major A, MN-major B> (wgrad)",
+               timeit(lambda: gemm(a, b, c, a_kmajor=False, b_kmajor=False, impl=impl)), flops=fl)
     report("cublas bf16 (torch.matmul)", timeit(lambda: torch.matmul(a, b.t(), out=c)), flops=fl)
 
 

@@ -54,7 +54,8 @@ def _worker(rank, world, port, q):
                           WORLD_SIZE=str(group_size))
         dist.init_process_group(
             "nccl", store=dist.PrefixStore("c10d", TCPStore("127.0.0.1", group_port, is_master=False, wait_for_workers=False)),
-            rank=group_rank, world_size=group_size, device_id=torch.device("cuda", rank))
+            rank=group_rank, world_size=group_size)  # no device_id: groups created later (the managed
+        # replicate dimension) would inherit it, and c10d then asks the group for a native CUDA backend
 
         torch.manual_seed(0)
         model = nn.Sequential(nn.Linear(128, 256, bias=False), nn.Tanh(), nn.Linear(256, 64, bias=False)).cuda()
@@ -83,7 +84,8 @@ def _worker(rank, world, port, q):
             grads = [p.grad.to_local().clone() for p in model.parameters()]
             optimizer.step()  # should_commit, then the wrapped step
             torch.cuda.synchronize()
-            assert manager.current_step() == step and manager.errored() is None
+            assert manager.errored() is None, f"step {step}: {manager.errored()!r}"
+            assert manager.current_step() == step, (manager.current_step(), step)
         assert manager.num_participants() == 2
 
         # the same gradient, computed here from all four batches without any sharding

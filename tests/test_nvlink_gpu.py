@@ -227,12 +227,14 @@ def _host_gives_up_first(rank, world, port):
     )
     # step 1 (quorum, first configuration, initial weight sync) gets a generous host budget
     manager._timeout = timedelta(seconds=30)
-    manager.start_quorum()
-    t = torch.ones(1024, device="cuda")
-    manager.allreduce(t).wait()
-    assert manager.should_commit()
-    assert torch.all(t == 1.0).item()
-    # step 2: rank 1 joins the quorum but stays away from the allreduce (a host-side decision)
+    for step in (1, 2):
+        manager.start_quorum()
+        t = torch.ones(1024, device="cuda")
+        manager.allreduce(t).wait()
+        assert manager.should_commit()
+        # step 1 is the initial weight sync: the healing replica counts as a participant but sends zeros
+        assert torch.all(t == (0.5 if step == 1 else 1.0)).item(), t[:4]
+    # step 3: rank 1 joins the quorum but stays away from the allreduce (a host-side decision)
     manager._timeout = timedelta(seconds=1)
     manager.start_quorum()
     manager.wait_quorum()
@@ -547,6 +549,118 @@ def _diloco_outer(rank, world, port):
 def test_diloco_outer_step_single_kernel_two_gpus():
     _need_gpus(2)
     _spawn(_diloco_outer, 2)
+
+
+def _gemm_rs(rank, world, port):
+    """Weight-gradient GEMM fused with the reduce-scatter against the fp32 sum of all ranks' products."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, SymmetricHeap
+
+    heap = SymmetricHeap.get(1 << 30)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=20))
+    comm.configure(PrefixStore("grs", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)), rank, world, 0)
+
+    def inputs(tokens, rows, cols, seed):
+        out = []
+        for r in range(world):
+            g = torch.Generator(device="cuda").manual_seed(seed + r)
+            out.append((torch.randn(tokens, rows, device="cuda", generator=g).to(torch.bfloat16),
+                        torch.randn(tokens, cols, device="cuda", generator=g).mul(0.1).to(torch.bfloat16)))
+        return out
+
+    # (tokens, rows of the weight, columns); the first call needs the largest staging area
+    for case, (tokens, rows, cols) in enumerate([(1024, 1024 * world, 1024), (512, 256 * world, 512), (200, 128 * world, 256)]):
+        assert comm.can_fuse_wgrad(rows, cols)
+        everyone = inputs(tokens, rows, cols, 10 * case)
+        dy, x = everyone[rank]
+        ref = sum(d.float().t() @ xx.float() for d, xx in everyone)
+        share = rows // world
+        mine = ref[rank * share : (rank + 1) * share]
+        out = torch.empty(share, cols, device="cuda", dtype=torch.bfloat16)
+        comm.wgrad_reduce_scatter(dy, x, out)
+        torch.cuda.synchronize()
+        comm.check()
+        err = ((out.float() - mine).norm() / mine.norm()).item()
+        assert err < 4e-3, f"case {case}: relative error {err}"
+        # a second micro-batch accumulates into the shard
+        comm.wgrad_reduce_scatter(dy, x, out, accumulate=True)
+        torch.cuda.synchronize()
+        comm.check()
+        err = ((out.float() - 2 * mine).norm() / mine.norm()).item()
+        assert err < 8e-3, f"case {case}: relative error after accumulation {err}"
+    return "ok"
+
+
+def test_wgrad_gemm_fused_with_reduce_scatter_two_gpus():
+    _need_gpus(2)
+    _spawn(_gemm_rs, 2)
+
+
+def test_wgrad_gemm_fused_with_reduce_scatter_four_gpus():
+    _need_gpus(4)
+    _spawn(_gemm_rs, 4)
+
+
+def _hsdp_fused_rs(rank, world, port):
+    """Row-sharded projection matrices whose gradients are reduce-scattered inside the weight-gradient
+    GEMM: same parameters after three steps as one GPU fed the concatenated batch."""
+    from torch.distributed import PrefixStore, TCPStore
+
+    from torchft_b200.models.llama import Llama, LlamaConfig
+    from torchft_b200.parallel.hsdp import HSDPEngine
+    from torchft_b200.parallel.nvlink import NVLinkCommunicator, NVLinkShardComm, SymmetricHeap
+
+    cfg = LlamaConfig.tiny(dim=512, n_heads=4, n_kv_heads=2, ffn_dim=1024)
+    heap = SymmetricHeap.get(1 << 30)
+    store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
+    comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=30))
+    comm.bind(PrefixStore("frs", store), rank, world, "shard")
+    rs = NVLinkCommunicator(heap, timeout=timedelta(seconds=30))
+    rs.bind(PrefixStore("frs", store), rank, world, "rs")
+    calls = {"n": 0}
+    inner = rs.wgrad_reduce_scatter
+
+    def counted(*a, **kw):
+        calls["n"] += 1
+        return inner(*a, **kw)
+
+    rs.wgrad_reduce_scatter = counted
+    gen = torch.Generator().manual_seed(5)
+    tokens = torch.randint(cfg.vocab_size, (world, 256), generator=gen).cuda()
+    targets = torch.randint(cfg.vocab_size, (world, 256), generator=gen).cuda()
+    ref_model = Llama(cfg, device="cuda")
+    ref_model.init_weights(seed=3)
+    ref = HSDPEngine(ref_model, ref_model.units(), lr=1e-3)
+    model = Llama(cfg, device="cuda")
+    model.init_weights(seed=3)
+    engine = HSDPEngine(model, model.units(per_weight=True), shard_comm=NVLinkShardComm(comm, gather_engine="copy"),
+                        lr=1e-3, alloc=heap.alloc, fused_rs_comm=rs)
+    assert sum(u.fused_rs for u in engine.units) == 4 * cfg.n_layers
+    steps = 3
+    for _ in range(steps):
+        ref.train_step(tokens, targets)
+        engine.train_step(tokens[rank : rank + 1], targets[rank : rank + 1])
+    torch.cuda.synchronize()
+    comm.check()
+    rs.check()
+    assert calls["n"] == steps * 4 * cfg.n_layers, calls
+    engine.gather_parameters()
+    torch.cuda.synchronize()
+    for (name, p), (_, q) in zip(model.named_parameters(), ref_model.named_parameters()):
+        err = (p.float() - q.float()).abs().max().item()
+        assert err < 2e-2, f"{name}: sharded and single-GPU parameters differ by {err}"
+    return "ok"
+
+
+def test_hsdp_engine_fused_reduce_scatter_matches_single_gpu():
+    _need_gpus(2)
+    _spawn(_hsdp_fused_rs, 2)
+
+
+def test_hsdp_engine_fused_reduce_scatter_four_gpus():
+    _need_gpus(4)
+    _spawn(_hsdp_fused_rs, 4)
 
 
 def _hsdp_fused_gather(rank, world, port):

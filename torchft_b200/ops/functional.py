@@ -32,6 +32,10 @@ class _Linear(torch.autograd.Function):
     If the weight carries ``gather_comm`` (an ``NVLinkCommunicator``) and ``gather_pending`` is
     set, the forward product runs through the all-gather fused GEMM, which also completes the
     local copy of the weight for the backward products.
+
+    If the weight carries ``rs_comm`` (an ``NVLinkCommunicator``), its rows are sharded over that
+    group and the weight-gradient product runs through the GEMM fused with the reduce-scatter:
+    only this rank's rows of ``main_grad`` receive the gradient, already summed over the group.
     """
 
     @staticmethod
@@ -65,7 +69,16 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             weight = ctx.weight
             main_grad = getattr(weight, "main_grad", None)
-            if main_grad is not None:
+            rs_comm = getattr(weight, "rs_comm", None)
+            if main_grad is not None and rs_comm is not None:
+                # rows of the weight are sharded over the GPUs of the group: the GEMM's epilogue sends
+                # every tile to its owner, and only this rank's rows of the summed gradient are written
+                acc = bool(getattr(weight, "main_grad_initialized", False))
+                rows = weight.shape[0] // rs_comm.world
+                own = main_grad[rs_comm.rank * rows : (rs_comm.rank + 1) * rows]
+                rs_comm.wgrad_reduce_scatter(dy2, x2, own, accumulate=acc)
+                weight.main_grad_initialized = True
+            elif main_grad is not None:
                 acc = bool(getattr(weight, "main_grad_initialized", False))
                 gemm(dy2, x2, main_grad, a_kmajor=False, b_kmajor=False, accumulate=acc)  # dY^T @ X
                 weight.main_grad_initialized = True

@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 
-DEFAULT_IMPL = os.environ.get("TFT_GEMM", "single")
+DEFAULT_IMPL = os.environ.get("TFT_GEMM", "pair")
 assert DEFAULT_IMPL in ("single", "pair"), f"TFT_GEMM must be 'single' or 'pair', not {DEFAULT_IMPL!r}"
 
 

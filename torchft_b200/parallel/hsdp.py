@@ -50,6 +50,7 @@ class Unit:
     offset: int  # start inside the flat buffers (elements)
     numel: int  # padded length (multiple of ALIGN * shard_world)
     fused_gather: bool = False  # its all-gather happens inside the GEMM that first uses it
+    fused_rs: bool = False  # its reduce-scatter happens inside the weight-gradient GEMM
 
 
 class ShardComm:
@@ -87,6 +88,7 @@ class HSDPEngine:
         weight_decay: float = 0.1,
         alloc: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None,
         fused_gather_comm=None,
+        fused_rs_comm=None,
     ) -> None:
         """
         Args:
@@ -99,6 +101,10 @@ class HSDPEngine:
                 Units that consist of ONE matrix ``[N, K]`` marked ``linear_weight`` by the model, with ``N % (256 * shard_world) == 0`` and
                 ``K % 64 == 0`` (``Llama.units(per_weight=True)``) then skip the all-gather kernel:
                 their rows are gathered inside the first GEMM that uses the weight in a step
+            fused_rs_comm: an ``NVLinkCommunicator`` of the shard group (again a channel of its own).
+                Units that consist of ONE ``linear_weight`` matrix ``[N, K]`` with ``N % (128 * shard_world) == 0``
+                and ``K % 256 == 0`` get their gradient reduce-scattered inside the weight-gradient GEMM
+                (``NVLinkCommunicator.wgrad_reduce_scatter``); no reduce-scatter kernel runs for them
         """
         self.model = model
         self.manager = manager
@@ -163,6 +169,20 @@ class HSDPEngine:
                     u.params[0].gather_comm = fused_gather_comm
                     u.params[0].gather_pending = False
                     self._fused_units.append(u)
+        self._rs_comm = fused_rs_comm if S > 1 else None
+        if self._rs_comm is not None:
+            biggest = (0, 0)
+            for u in self.units:
+                if len(u.params) != 1 or u.params[0].dim() != 2 or not getattr(u.params[0], "linear_weight", False):
+                    continue
+                n_rows, k = u.params[0].shape
+                if self._rs_comm.can_fuse_wgrad(n_rows, k) and u.numel == n_rows * k:
+                    u.fused_rs = True
+                    u.params[0].rs_comm = self._rs_comm
+                    if n_rows * k > biggest[0] * biggest[1]:
+                        biggest = (n_rows, k)
+            if biggest[0]:
+                self._rs_comm.reserve_wgrad_staging(*biggest)
         self._synced: set = set()
         self._futures: list = []
         if hasattr(model, "unit_grad_ready"):
@@ -208,7 +228,7 @@ class HSDPEngine:
         self.comm_stream.wait_stream(current)
         with torch.cuda.stream(self.comm_stream):
             full = self.flat_grad[u.offset : u.offset + u.numel]
-            if self.comm.world > 1:
+            if self.comm.world > 1 and not u.fused_rs:  # fused_rs: the wgrad GEMM already left the sum in the own slice
                 self.comm.reduce_scatter_(full, self._shard_numel(u))
             if self.manager is not None:
                 self._futures.append(self.manager.allreduce(self._own(self.flat_grad, u)))
@@ -234,6 +254,8 @@ class HSDPEngine:
                 probes.append(("shard-group collective", self.comm.status_async()))
             if self._fused_comm is not None:
                 probes.append(("fused all-gather GEMM", self._fused_comm.status_async()))  # ran on this stream
+            if self._rs_comm is not None:
+                probes.append(("weight-gradient GEMM fused with reduce-scatter", self._rs_comm.status_async()))
         for f in self._futures:
             f.wait()
         self._futures = []
@@ -359,8 +381,9 @@ class HSDPEngine:
             # collective that the other side completed or never started).
             torch.cuda.synchronize(self.device)
             self.comm.renew()
-            if self._fused_comm is not None and getattr(self._fused_comm, "_bound", None) is not None:
-                self._fused_comm.renew()
+            for extra in (self._fused_comm, self._rs_comm):
+                if extra is not None and getattr(extra, "_bound", None) is not None:
+                    extra.renew()
         return loss.detach()
 
     # ------------------------------------------------------------------ state for live recovery

@@ -65,6 +65,7 @@ def _lib_p2p() -> ctypes.CDLL:
             "tft_p2p_broadcast": head + [L, L, I, I, P],
             "tft_p2p_barrier": head + [P],
             "tft_ag_gemm_bf16": head + [P, L, P, I, I, I, I, I, P, I, P],
+            "tft_gemm_rs_bf16": head + [P, P, P, I, I, I, I, I, I, L, L, I, P],
             "tft_diloco_outer": head + [L, L, P, P, P, P, L, I, F, F, F, I, I, I, P, I, P],
         }.items():
             fn = getattr(lib, name)
@@ -241,6 +242,8 @@ class NVLinkCommunicator:
         self._bound: Optional[Tuple[Store, str]] = None
         self._generation = 0
         self._status_pinned: Optional[torch.Tensor] = None
+        self._rs_stage: Optional[torch.Tensor] = None  # staging area of the wgrad GEMM fused with reduce-scatter
+        self._rs_flags: Optional[torch.Tensor] = None
         self._block_ready: Optional[torch.Tensor] = None  # per-block counters of the fused all-gather GEMM
         self._phase_flag: Optional[torch.Tensor] = None  # phase word of the fused DiLoCo outer step
 
@@ -454,6 +457,53 @@ class NVLinkCommunicator:
         _lib.count_launch()
         return out.view(*x.shape[:-1], N)
 
+    def wgrad_reduce_scatter(self, dy: torch.Tensor, x: torch.Tensor, out_rows: torch.Tensor,
+                             accumulate: bool = False) -> None:
+        """``out_rows (+)= (sum over ranks of dy.T @ x)[rows of this rank]`` in ONE kernel.
+
+        ``dy [tokens, M]`` and ``x [tokens, N]`` are this rank's local bf16 activations; the product
+        ``dy.T @ x`` is the weight gradient ``[M, N]`` of a linear layer whose rows are sharded over the
+        ranks of this communicator, and ``out_rows [M / world, N]`` is this rank's shard of it.  The
+        tcgen05 GEMM's epilogue sends every tile to the rank that owns it and the owner adds the
+        partial tiles up in fp32 (``csrc/kernels/gemm_rs.cu``), so neither the full local product nor a
+        separate reduce-scatter exists.  Needs ``M % (128 * world) == 0`` and ``N % 256 == 0``
+        (``can_fuse_wgrad``); runs on the current stream; use a communicator (channel) of its own.
+        """
+        assert dy.dtype == x.dtype == out_rows.dtype == torch.bfloat16
+        assert dy.dim() == 2 and x.dim() == 2 and dy.shape[0] == x.shape[0]
+        assert dy.stride(1) == 1 and x.stride(1) == 1 and out_rows.stride(1) == 1
+        K, M = dy.shape
+        N = x.shape[1]
+        assert self.can_fuse_wgrad(M, N) and tuple(out_rows.shape) == (M // self.world, N)
+        lib = _lib_p2p()
+        need = M * N
+        if self._rs_stage is None or self._rs_stage.numel() < need:
+            # grows to the largest weight seen; allocate the largest one first to avoid waste
+            self._rs_stage = self.heap.alloc(need, torch.bfloat16)
+        flags = (M // 128) * (N // 256)
+        if self._rs_flags is None or self._rs_flags.numel() < flags:
+            self._rs_flags = self.heap.alloc(max(flags, 8192), torch.int32)
+        code = lib.tft_gemm_rs_bf16(
+            *self._head(), dy.data_ptr(), x.data_ptr(), out_rows.data_ptr(), M, N, K, dy.stride(0), x.stride(0),
+            out_rows.stride(0), self._offset(self._rs_stage), self._offset(self._rs_flags), 1 if accumulate else 0,
+            _lib.stream_ptr())
+        _lib.check(code, "tft_gemm_rs_bf16")
+        _lib.count_launch()
+
+    def can_fuse_wgrad(self, rows: int, cols: int) -> bool:
+        """Whether a weight ``[rows, cols]`` meets the tiling rules of ``wgrad_reduce_scatter``."""
+        return self.world > 1 and rows % (128 * self.world) == 0 and cols % 256 == 0
+
+    def reserve_wgrad_staging(self, rows: int, cols: int) -> None:
+        """Allocates the staging area and flags for weights up to ``[rows, cols]`` now.  The heap is a
+        bump allocator and every rank must allocate the same things in the same order, so do this once,
+        on every rank, with the largest weight, before training."""
+        if self._rs_stage is None or self._rs_stage.numel() < rows * cols:
+            self._rs_stage = self.heap.alloc(rows * cols, torch.bfloat16)
+        flags = max((rows // 128) * (cols // 256), 8192)
+        if self._rs_flags is None or self._rs_flags.numel() < flags:
+            self._rs_flags = self.heap.alloc(flags, torch.int32)
+
     def diloco_outer_(self, local: torch.Tensor, grad: torch.Tensor, global_in: torch.Tensor, mom_in: torch.Tensor,
                       global_out: torch.Tensor, mom_out: torch.Tensor, *, inv_n: float, lr: float, momentum: float,
                       nesterov: bool, first: bool, contribute: bool = True) -> None:
@@ -593,8 +643,10 @@ class ProcessGroupNVLink(ProcessGroup):
     # -- c10d surface
     def allreduce(self, tensors: List[torch.Tensor], opts: object) -> Work:
         op = opts.reduceOp if hasattr(opts, "reduceOp") else opts
-        if op not in (ReduceOp.SUM, ReduceOp.AVG):
-            raise NotImplementedError("torchft-nvlink supports SUM and AVG")
+        # explicit comparisons: ``op in (SUM, AVG)`` asks the enum member first, and that one does not
+        # recognise the ReduceOp object an AllreduceOptions carries
+        if not (op == ReduceOp.SUM or op == ReduceOp.AVG):
+            raise NotImplementedError(f"torchft-nvlink supports SUM and AVG, not {op}")
         scale = 1.0 / self._comm.world if op == ReduceOp.AVG else 1.0
         return self._launch(tensors, lambda b: self._comm.allreduce_(b, scale), "allreduce")
 

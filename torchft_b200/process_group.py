@@ -449,7 +449,8 @@ class ManagedProcessGroup(ProcessGroupWrapper):
             return _DummyWork(tensors)
         try:
             op = opts.reduceOp if hasattr(opts, "reduceOp") else opts
-            if len(tensors) == 1 and op in (ReduceOp.SUM, ReduceOp.AVG):
+            # (``op in (SUM, AVG)`` would compare the enum member first, which does not know ReduceOp objects)
+            if len(tensors) == 1 and (op == ReduceOp.SUM or op == ReduceOp.AVG):
                 # A replica that is still healing (or a spare) is a member of the group but its data
                 # must not count, and an average is over the participants, not over the members:
                 # both are what allreduce_scaled expresses (the reference hands ``opts`` to the
