@@ -55,9 +55,15 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--fused-rs", action="store_true",
                     help="shard every projection matrix by rows and reduce-scatter its gradient inside the "
                          "weight-gradient GEMM (no reduce-scatter kernel for those matrices)")
-    ap.add_argument("--gather-engine", default="sm", choices=["sm", "copy", "copy-push"],
+    ap.add_argument("--gather-engine", default="copy", choices=["sm", "copy", "copy-push"],
                     help="parameter all-gather inside a replica group: one SM kernel per unit, or the copy engines "
                          "(pull / push) between two barrier kernels")
+    ap.add_argument("--reduce-engine", default="copy", choices=["sm", "copy"],
+                    help="gradient reduce-scatter inside a replica group: one SM kernel per unit that loads over NVLink, "
+                         "or copy-engine pulls into local staging plus a local sum kernel")
+    ap.add_argument("--allreduce-engine", default="copy", choices=["sm", "copy"],
+                    help="cross-replica gradient allreduce of buffers >= 8 MiB: the fused peer-load kernel, or the copy "
+                         "engines plus a local sum kernel")
     ap.add_argument("--ref-init", default="resume", choices=["resume", "heal"],
                     help="reference arm only: 'resume' starts every replica group from the same seed and the same "
                          "manager step (no step-0 heal); 'heal' lets group 0 serve its state over HTTP at step 0")
@@ -202,7 +208,8 @@ def run_ours(args: argparse.Namespace) -> None:
 
     model = Llama(cfg, device=device)
     model.init_weights(seed=1234)  # identical on every rank, as after the step-0 heal
-    pg = ProcessGroupNVLink(timeout=timedelta(seconds=60), heap=heap, staging_bytes=64 << 20)
+    pg = ProcessGroupNVLink(timeout=timedelta(seconds=60), heap=heap, staging_bytes=64 << 20,
+                            copy_engine_min_bytes=(8 << 20) if args.allreduce_engine == "copy" else None)
     engine_box = {}
     manager = Manager(
         pg=pg,
@@ -231,13 +238,13 @@ def run_ours(args: argparse.Namespace) -> None:
         fused_rs = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
         fused_rs.bind(client_store, shard_rank, shard_world, "fused_rs")
     engine = HSDPEngine(
-        model, model.units(per_weight=fused is not None or fused_rs is not None), fused_rs_comm=fused_rs, manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine),
+        model, model.units(per_weight=fused is not None or fused_rs is not None), fused_rs_comm=fused_rs, manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine, reduce_engine=args.reduce_engine),
         lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,
     )
     engine_box["engine"] = engine
 
     # ---- data: synthetic token ids in pinned host memory, a fresh batch every step
-    total_steps = args.warmup + 2 * args.steps
+    total_steps = args.warmup + 2 * args.steps + 8  # a few spare batches for the optional timing pass
     gen = torch.Generator().manual_seed(1000 + rank)
     host_tokens = torch.randint(cfg.vocab_size, (total_steps, batch, seq), generator=gen).pin_memory()
     host_targets = torch.randint(cfg.vocab_size, (total_steps, batch, seq), generator=gen).pin_memory()
@@ -297,6 +304,16 @@ def run_ours(args: argparse.Namespace) -> None:
         device_ms, e2e_max = float(t[0]), float(t[1])
         e2e_s = e2e_max if e2e_s is not None else None
 
+    if os.environ.get("TFT_ENGINE_TIMING"):
+        # optional diagnosis, after everything that is reported has been measured
+        engine.timing = []
+        for _ in range(5):
+            one_step(True)
+        if rank == 0:
+            keys = sorted({k for row in engine.timing for k in row})
+            print(json.dumps({"engine_timing_ms": {k: round(statistics.median(r.get(k, 0.0) for r in engine.timing), 3)
+                                                   for k in keys}}), file=sys.stderr, flush=True)
+        engine.timing = None
     _lib.check_status("bench")
     tokens_per_step = args.gpus * batch * seq
     ms_per_step = device_ms / args.steps
@@ -328,7 +345,9 @@ def run_ours(args: argparse.Namespace) -> None:
                 "parameter_gather": ("inside the first GEMM of each projection (all-gather fused GEMM)" if fused is not None
                                      else f"per-unit all-gather ({args.gather_engine}) overlapped with forward"),
                 "gradient_reduce_scatter": ("inside the weight-gradient GEMM of every projection matrix" if fused_rs is not None
-                                            else "one kernel per unit after its backward"),
+                                            else f"per unit after its backward ({args.reduce_engine})"),
+                "cross_replica_allreduce": ("copy engines + local sum kernel for buffers >= 8 MiB" if args.allreduce_engine == "copy"
+                                            else "fused peer-memory kernel (sum, 1/n, broadcast in one pass)"),
                 "l2_policy": "no flush needed: weights, gradients and activations streamed per step exceed 100 GB (L2 is 126 MB)",
             },
             "clocks": clocks,

@@ -83,6 +83,23 @@ def _collectives(rank, world, port):
             ref = sum(v.to(dtype).float() for r, v in enumerate(vals) if r != 0)
             err = (t.float() - ref).abs().max().item()
             assert err < (4e-2 if dtype == torch.bfloat16 else 1e-5), ("contrib", dtype, n, err)
+    # allreduce with the copy engines moving the data: same result as the kernel to rounding
+    big = NVLinkCommunicator(heap, timeout=timedelta(seconds=20), copy_engine_min_bytes=1 << 16)
+    big.configure(PrefixStore("t1ce", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)), rank, world, 0)
+    for dtype, n in ((torch.bfloat16, (1 << 20) + 8 * 3), (torch.float32, 1 << 18)):
+        t = heap.alloc(n, dtype)
+        vals = [torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(99 + r)) for r in range(world)]
+        t.copy_(vals[rank].to(dtype))
+        big.allreduce_(t, 1.0 / world)
+        ref = sum(v.to(dtype).float() for v in vals) / world
+        err = (t.float() - ref).abs().max().item()
+        assert err < (2e-2 if dtype == torch.bfloat16 else 1e-5), ("copy engine", dtype, err)
+        t.copy_(vals[rank].to(dtype))
+        big.allreduce_(t, 1.0, contribute=(rank != 0))
+        ref = sum(v.to(dtype).float() for r, v in enumerate(vals) if r != 0)
+        err = (t.float() - ref).abs().max().item()
+        assert err < (4e-2 if dtype == torch.bfloat16 else 1e-5), ("copy engine, muted rank", dtype, err)
+    big.check()
     # reduce-scatter + all-gather == allreduce
     n = world * 4096
     full = heap.alloc(n, torch.bfloat16)
@@ -92,6 +109,12 @@ def _collectives(rank, world, port):
     ref = sum(v.float() for v in vals)
     sl = slice(rank * 4096, (rank + 1) * 4096)
     assert (full[sl].float() - ref[sl]).abs().max().item() < 4e-2
+    # copy-engine variant: same summation order, so the same bits
+    by_kernel = full[sl].clone()
+    comm.barrier()  # everybody has read what it needed before the buffers are refilled
+    full.copy_(vals[rank])
+    comm.reduce_scatter_(full, 1.0, engine="copy")
+    assert torch.equal(full[sl], by_kernel)
     comm.all_gather_(full)
     assert (full.float() - ref).abs().max().item() < 4e-2
     # the same exchange by the copy engines, pulled and pushed

@@ -253,6 +253,35 @@ def test_managed_process_group():
     assert isinstance(pg.allreduce([t], ReduceOp.SUM), _DummyWork)
 
 
+def test_managed_process_group_averages_over_participants_and_mutes_a_healing_replica():
+    """c10d hands the reduction as a ReduceOp object inside AllreduceOptions (that is what FSDP2 does);
+    AVG must divide by the participants, and a replica that is still healing must add zeros."""
+    store = make_store()
+    inner = ProcessGroupGloo()
+    inner.configure(f"127.0.0.1:{store.port}/managed_avg", 0, 1)
+    manager = create_autospec(Manager)
+    manager.errored.return_value = None
+    manager._pg = inner
+    manager.num_participants.return_value = 4
+    manager.is_participating.return_value = True
+    manager.wrap_future.side_effect = lambda fut, default: fut
+    pg = ManagedProcessGroup(manager)
+    opts = AllreduceOptions()
+    opts.reduceOp = ReduceOp.AVG
+    t = torch.full((8,), 6.0)
+    pg.allreduce([t], opts).wait()
+    assert torch.allclose(t, torch.full((8,), 1.5))  # one member, four participants
+    opts.reduceOp = ReduceOp.SUM
+    t = torch.full((8,), 6.0)
+    pg.allreduce([t], opts).wait()
+    assert torch.allclose(t, torch.full((8,), 6.0))
+    manager.is_participating.return_value = False
+    t = torch.full((8,), 6.0)
+    pg.allreduce([t], opts).wait()
+    assert torch.equal(t, torch.zeros(8))
+    assert manager.report_error.call_count == 0
+
+
 def test_register_for_functional_collectives(tmp_path):
     """A registered group resolves through c10d's registry (needs a default group)."""
     store = make_store()

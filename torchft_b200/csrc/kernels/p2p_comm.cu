@@ -167,6 +167,31 @@ reduce_scatter_kernel(Comm c, size_t off, long long slice_vec, float scale) {
   finish(c, flag);
 }
 
+// Local half of the copy-engine reduce-scatter: own slice + (world - 1) staged slices, summed in the
+// same order as reduce_scatter_kernel (own first, then rank+1, rank+2, ...), so both give the same bits.
+template <typename T>
+__global__ void __launch_bounds__(512)
+sum_staged_kernel(uint8_t* __restrict__ own, const uint8_t* __restrict__ staged, long long slice_vec, int others,
+                  float scale) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < slice_vec; i += stride) {
+    uint4 in[MAX_RANKS];
+    in[0] = *reinterpret_cast<const uint4*>(own + i * 16);
+#pragma unroll
+    for (int k = 1; k < MAX_RANKS; ++k) {
+      if (k > others) break;
+      in[k] = *reinterpret_cast<const uint4*>(staged + (static_cast<size_t>(k - 1) * slice_vec + i) * 16);
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k > others) break;
+      Vec<T>::add(acc, in[k]);
+    }
+    *reinterpret_cast<uint4*>(own + i * 16) = Vec<T>::pack(acc, scale);
+  }
+}
+
 __global__ void __launch_bounds__(512)
 all_gather_kernel(Comm c, size_t off, long long slice_vec) {
   __shared__ int flag[2];
@@ -482,6 +507,96 @@ TFT_API int tft_p2p_all_gather(void* const* heaps, int rank, int world, unsigned
   return static_cast<int>(cudaGetLastError());
 }
 
+// Reduce-scatter with the data movement on the copy engines: a barrier kernel (one block; every
+// rank's buffer is final), world - 1 cudaMemcpyAsync pulls of this rank's slice out of the peers'
+// buffers into a local staging area (`stage`, (world - 1) * slice_bytes, need not be in the heap), a
+// local kernel that adds own + staged slices in fp32 and scales, and -- if `closing` -- a second
+// barrier after which the peers may overwrite their buffers.  SMs only run the local sum, which is
+// bound by this GPU's HBM and short; nothing spins on NVLink loads beside the GEMMs.
+// Takes sequence numbers seq (and seq + 1 with `closing`).
+TFT_API int tft_p2p_reduce_scatter_ce(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq,
+                                      int timeout_ms, const int* abort_word, int* status, long long off,
+                                      long long slice_bytes, int dtype, float scale, void* stage, int closing,
+                                      int max_blocks, cudaStream_t stream) {
+  if ((off | slice_bytes) & 15 || (reinterpret_cast<uintptr_t>(stage) & 15)) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const size_t mine = static_cast<size_t>(off) + static_cast<size_t>(rank) * static_cast<size_t>(slice_bytes);
+  for (int k = 1; k < world; ++k) {
+    const int p = (rank + k) % world;
+    e = cudaMemcpyAsync(static_cast<uint8_t*>(stage) + static_cast<size_t>(k - 1) * slice_bytes, c.heap[p] + mine,
+                        static_cast<size_t>(slice_bytes), cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const long long nvec = slice_bytes / 16;
+  const int grid = grid_for(nvec, max_blocks);
+  if (dtype == 0)
+    sum_staged_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(c.heap[rank] + mine, static_cast<const uint8_t*>(stage),
+                                                               nvec, world - 1, scale);
+  else
+    sum_staged_kernel<float><<<grid, 512, 0, stream>>>(c.heap[rank] + mine, static_cast<const uint8_t*>(stage), nvec,
+                                                       world - 1, scale);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || !closing) return static_cast<int>(e);
+  c.seq = seq + 1;
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Allreduce (+ scale) with the data movement on the copy engines, for buffers large enough that
+// three one-block barriers do not matter: two-shot like allreduce_kernel, i.e. rank r reduces chunk r
+// and everybody collects the reduced chunks.
+//   barrier | pull chunk r of every peer into `stage` | local sum of own + staged, scaled, into own chunk r
+//   barrier | pull the reduced chunk p from every peer p into the own buffer | barrier
+// `stage`: (world - 1) * ceil(nvec / world) * 16 bytes of local memory.  A rank that must not
+// contribute zeroes its buffer before the call (the host wrapper does).  Takes sequence numbers seq,
+// seq + 1 and seq + 2.
+TFT_API int tft_p2p_allreduce_ce(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq, int timeout_ms,
+                                 const int* abort_word, int* status, long long off, long long bytes, int dtype,
+                                 float scale, void* stage, int max_blocks, cudaStream_t stream) {
+  if ((off | bytes) & 15 || (reinterpret_cast<uintptr_t>(stage) & 15)) return -1;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  const long long nvec = bytes / 16;
+  const long long per = (nvec + world - 1) / world;
+  auto lo = [&](int r) { return per * r < nvec ? per * r : nvec; };  // chunk r = vectors [lo(r), lo(r + 1))
+  auto len = [&](int r) { return lo(r + 1) - lo(r); };
+  cudaError_t e;
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  const long long mine = len(rank);
+  if (mine > 0) {
+    for (int k = 1; k < world; ++k) {
+      const int p = (rank + k) % world;
+      e = cudaMemcpyAsync(static_cast<uint8_t*>(stage) + static_cast<size_t>(k - 1) * mine * 16,
+                          c.heap[p] + off + lo(rank) * 16, static_cast<size_t>(mine) * 16, cudaMemcpyDeviceToDevice, stream);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    const int grid = grid_for(mine, max_blocks);
+    if (dtype == 0)
+      sum_staged_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(c.heap[rank] + off + lo(rank) * 16,
+                                                                 static_cast<const uint8_t*>(stage), mine, world - 1, scale);
+    else
+      sum_staged_kernel<float><<<grid, 512, 0, stream>>>(c.heap[rank] + off + lo(rank) * 16,
+                                                         static_cast<const uint8_t*>(stage), mine, world - 1, scale);
+    if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  }
+  c.seq = seq + 1;
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
+  for (int k = 1; k < world; ++k) {
+    const int p = (rank + k) % world;
+    if (len(p) <= 0) continue;
+    e = cudaMemcpyAsync(c.heap[rank] + off + lo(p) * 16, c.heap[p] + off + lo(p) * 16, static_cast<size_t>(len(p)) * 16,
+                        cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  c.seq = seq + 2;
+  barrier_kernel<<<1, 32, 0, stream>>>(c);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // All-gather by the copy engines: a barrier kernel (one block), world - 1 peer copies issued with
 // cudaMemcpyAsync, a second barrier kernel.  No SM moves data, so a GEMM that runs beside it keeps
 // its SMs, its issue slots and its share of the power budget.  `pull` != 0: this rank copies every
@@ -553,6 +668,14 @@ TFT_API int tft_p2p_pull(void* dst, const void* src, long long bytes, int max_bl
       static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nvec);
   return static_cast<int>(cudaGetLastError());
 }
+
+// The same copy by a copy engine instead of SMs: one cudaMemcpyAsync from the peer's mapped heap.
+// Large transfers run at the link rate this way and leave the SMs alone; no alignment rule.
+TFT_API int tft_p2p_pull_ce(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  return static_cast<int>(cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, stream));
+}
+
 
 // DiLoCo outer step fused with its allreduce (see diloco_outer_kernel).  `off_local` / `off_g` are heap
 // offsets of the local weights and of the gradient buffer (n elements each, 16-byte aligned, padded

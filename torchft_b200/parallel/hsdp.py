@@ -360,6 +360,7 @@ class HSDPEngine:
     # ------------------------------------------------------------------ whole step
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One fault-tolerant training step; returns the (local) loss tensor."""
+        marks = self._timing_marks() if self.timing is not None else None
         if self.manager is not None:
             self.manager.start_quorum()
         # Updated slices are exchanged at the START of a step, on every rank, whether or not it (or a
@@ -370,12 +371,25 @@ class HSDPEngine:
         self.zero_grad()
         loss = self.model(tokens, targets)
         self._finish_gather()
+        if marks is not None:
+            marks("forward")
         loss.backward()
+        if marks is not None:
+            marks("backward")
         self.sync_gradients()
+        if marks is not None:
+            marks("gradient_sync_tail")
         grad_scale = 1.0 / self.comm.world  # reduce-scatter sums over the shard group
-        if self.manager is None or self.manager.should_commit():
+        committed = self.manager is None or self.manager.should_commit()
+        if marks is not None:
+            marks("commit_vote", host=True)
+        if committed:
             self.optimizer_step(grad_scale)
-        elif self.comm.world > 1:
+            if marks is not None:
+                marks("optimizer_queued", final=True)
+        elif marks is not None:
+            marks("not_committed", final=True)
+        if not committed and self.comm.world > 1:
             # The vote is group-wide, so every rank of the group is here: all move to fresh flags and
             # sequence numbers, whichever of them saw the failure (one side may have given up on a
             # collective that the other side completed or never started).
@@ -385,6 +399,40 @@ class HSDPEngine:
                 if extra is not None and getattr(extra, "_bound", None) is not None:
                     extra.renew()
         return loss.detach()
+
+    # ------------------------------------------------------------------ optional per-phase timing
+    timing: Optional[List[Dict[str, float]]] = None  # set to [] to collect one dict per step
+
+    def _timing_marks(self):
+        """Per-phase timing of one step (``engine.timing = []`` switches it on): device time between
+        events on the compute stream for the phases that queue GPU work, host time for the vote."""
+        import time as _time
+
+        stream = torch.cuda.current_stream(self.device)
+        events = []
+        host = [_time.perf_counter()]
+        first = torch.cuda.Event(enable_timing=True)
+        first.record(stream)
+        events.append(("start", first))
+        row: Dict[str, float] = {}
+
+        def mark(name: str, host_only: bool = False, final: bool = False, **kw) -> None:
+            host_only = host_only or kw.get("host", False)
+            now = _time.perf_counter()
+            row[f"{name}_host_ms"] = (now - host[0]) * 1e3
+            host[0] = now
+            if not host_only:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                events.append((name, ev))
+            if final:
+                events[-1][1].synchronize()
+                for (_, a), (n, b) in zip(events, events[1:]):
+                    row[f"{n}_device_ms"] = a.elapsed_time(b)
+                assert self.timing is not None
+                self.timing.append(row)
+
+        return mark
 
     # ------------------------------------------------------------------ state for live recovery
     def state_dict(self) -> Dict[str, object]:

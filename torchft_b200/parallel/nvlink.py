@@ -62,6 +62,8 @@ def _lib_p2p() -> ctypes.CDLL:
             "tft_p2p_reduce_scatter": head + [L, L, I, F, I, P],
             "tft_p2p_all_gather": head + [L, L, I, P],
             "tft_p2p_all_gather_ce": head + [L, L, I, P],
+            "tft_p2p_reduce_scatter_ce": head + [L, L, I, F, P, I, I, P],
+            "tft_p2p_allreduce_ce": head + [L, L, I, F, P, I, P],
             "tft_p2p_broadcast": head + [L, L, I, I, P],
             "tft_p2p_barrier": head + [P],
             "tft_ag_gemm_bf16": head + [P, L, P, I, I, I, I, I, P, I, P],
@@ -212,13 +214,17 @@ class _StreamWork(dist._Work):
 
 
 class NVLinkCommunicator:
-    def __init__(self, heap: SymmetricHeap, timeout: timedelta = timedelta(seconds=10), max_blocks: int = 64) -> None:
+    def __init__(self, heap: SymmetricHeap, timeout: timedelta = timedelta(seconds=10), max_blocks: int = 64,
+                 copy_engine_min_bytes: Optional[int] = None) -> None:
         """
         Args:
             timeout: budget of every device-side wait (a peer that does not show up within it
                 makes the collective fail with a status instead of hanging)
             max_blocks: thread blocks per collective kernel (SMs lent to communication)
+            copy_engine_min_bytes: allreduce buffers of at least this size move by the copy engines
+                (see ``allreduce_``); ``None`` keeps every size on the fused kernel
         """
+        self.copy_engine_min_bytes = copy_engine_min_bytes
         self.heap = heap
         self.device = heap.device
         self.channel = heap.new_channel()
@@ -242,6 +248,7 @@ class NVLinkCommunicator:
         self._bound: Optional[Tuple[Store, str]] = None
         self._generation = 0
         self._status_pinned: Optional[torch.Tensor] = None
+        self._rs_ce_stage: Optional[torch.Tensor] = None  # local staging of the copy-engine reduce-scatter
         self._rs_stage: Optional[torch.Tensor] = None  # staging area of the wgrad GEMM fused with reduce-scatter
         self._rs_flags: Optional[torch.Tensor] = None
         self._block_ready: Optional[torch.Tensor] = None  # per-block counters of the fused all-gather GEMM
@@ -370,7 +377,13 @@ class NVLinkCommunicator:
 
     # ------------------------------------------------------------------ collectives (on the current stream)
     def allreduce_(self, t: torch.Tensor, scale: float = 1.0, contribute: bool = True) -> None:
-        """In place on a heap tensor: ``t <- scale * sum over contributing ranks``."""
+        """In place on a heap tensor: ``t <- scale * sum over contributing ranks``.
+
+        Buffers of at least ``copy_engine_min_bytes`` (``None``: never) move by the copy engines between
+        one-block barrier kernels, with a short local kernel for the sum, instead of by the fused
+        peer-load kernel: slower in isolation for mid-sized buffers, but it leaves the SMs to the
+        GEMMs it overlaps with.  Every member must use the same threshold.
+        """
         if self.world == 1:
             if not contribute:
                 t.zero_()
@@ -381,13 +394,35 @@ class NVLinkCommunicator:
         assert nbytes % 16 == 0, "buffer length must be a multiple of 16 bytes"
         dtype = 0 if t.dtype == torch.bfloat16 else 1
         assert t.dtype in (torch.bfloat16, torch.float32)
+        if self.copy_engine_min_bytes is not None and nbytes >= self.copy_engine_min_bytes:
+            if not contribute:
+                t.zero_()  # rare (a healing replica): costs one pass over the buffer instead of a kernel variant
+            per = -(-(nbytes // 16) // self.world) * 16
+            need = per * (self.world - 1)
+            if self._rs_ce_stage is None or self._rs_ce_stage.numel() < need:
+                self._rs_ce_stage = torch.empty(need, dtype=torch.uint8, device=self.device)
+            head = self._head()
+            self.seq += 2
+            code = _lib_p2p().tft_p2p_allreduce_ce(*head, self._offset(t), nbytes, dtype, scale, self._rs_ce_stage.data_ptr(),
+                                                   148, _lib.stream_ptr())
+            _lib.check(code, "tft_p2p_allreduce_ce")
+            _lib.count_launch(4)
+            return
         code = _lib_p2p().tft_p2p_allreduce(*self._head(), self._offset(t), nbytes, dtype, scale, 1 if contribute else 0,
                                             self.max_blocks, _lib.stream_ptr())
         _lib.check(code, "tft_p2p_allreduce")
         _lib.count_launch()
 
-    def reduce_scatter_(self, full: torch.Tensor, scale: float = 1.0) -> None:
-        """``full`` holds ``world`` equal slices; rank r ends with ``scale * sum`` in slice r."""
+    def reduce_scatter_(self, full: torch.Tensor, scale: float = 1.0, engine: str = "sm", closing: bool = True) -> None:
+        """``full`` holds ``world`` equal slices; rank r ends with ``scale * sum`` in slice r.
+
+        ``engine="sm"``: one kernel loads the peers' copies of the slice over NVLink and adds them.
+        ``engine="copy"``: the copy engines pull the peers' copies into a local staging area between
+        barrier kernels and a short local kernel adds them (same summation order, same bits); the SMs
+        stay with whatever computes beside it.  ``closing=False`` drops the final barrier: the caller
+        then guarantees by other means that no peer overwrites its buffer while it may still be read
+        (``HSDPEngine`` does: the commit vote of the step follows every rank's collectives).
+        """
         if self.world == 1:
             if scale != 1.0:
                 full.mul_(scale)
@@ -395,10 +430,25 @@ class NVLinkCommunicator:
         slice_bytes = full.numel() * full.element_size() // self.world
         assert slice_bytes % 16 == 0
         dtype = 0 if full.dtype == torch.bfloat16 else 1
-        code = _lib_p2p().tft_p2p_reduce_scatter(*self._head(), self._offset(full), slice_bytes, dtype, scale,
-                                                 self.max_blocks, _lib.stream_ptr())
-        _lib.check(code, "tft_p2p_reduce_scatter")
-        _lib.count_launch()
+        if engine == "sm":
+            code = _lib_p2p().tft_p2p_reduce_scatter(*self._head(), self._offset(full), slice_bytes, dtype, scale,
+                                                     self.max_blocks, _lib.stream_ptr())
+            _lib.check(code, "tft_p2p_reduce_scatter")
+            _lib.count_launch()
+            return
+        if engine != "copy":
+            raise ValueError(f"unknown reduce-scatter engine {engine!r}")
+        need = slice_bytes * (self.world - 1)
+        if self._rs_ce_stage is None or self._rs_ce_stage.numel() < need:
+            self._rs_ce_stage = torch.empty(need, dtype=torch.uint8, device=self.device)  # local: no peer touches it
+        head = self._head()
+        if closing:
+            self.seq += 1
+        code = _lib_p2p().tft_p2p_reduce_scatter_ce(*head, self._offset(full), slice_bytes, dtype, scale,
+                                                    self._rs_ce_stage.data_ptr(), 1 if closing else 0, 148,
+                                                    _lib.stream_ptr())
+        _lib.check(code, "tft_p2p_reduce_scatter_ce")
+        _lib.count_launch(3 if closing else 2)
 
     def all_gather_(self, full: torch.Tensor, engine: str = "sm") -> None:
         """Every rank ends with all ``world`` slices of ``full``; on entry slice r of rank r is valid.
@@ -557,10 +607,11 @@ class ProcessGroupNVLink(ProcessGroup):
     """
 
     def __init__(self, timeout: timedelta = timedelta(seconds=10), heap: Optional[SymmetricHeap] = None,
-                 staging_bytes: int = 256 << 20, max_blocks: int = 64) -> None:
+                 staging_bytes: int = 256 << 20, max_blocks: int = 64, copy_engine_min_bytes: Optional[int] = None) -> None:
         super().__init__(0, 1)
         self._heap = heap if heap is not None else SymmetricHeap.get(max(staging_bytes * 2, 1 << 30))
-        self._comm = NVLinkCommunicator(self._heap, timeout=timeout, max_blocks=max_blocks)
+        self._comm = NVLinkCommunicator(self._heap, timeout=timeout, max_blocks=max_blocks,
+                                        copy_engine_min_bytes=copy_engine_min_bytes)
         self._staging = self._heap.alloc(staging_bytes, torch.uint8)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._configured = False
@@ -707,10 +758,13 @@ class ProcessGroupNVLink(ProcessGroup):
 class NVLinkShardComm:
     """Shard-dimension collectives of the HSDP engine over a fixed replica-group communicator."""
 
-    def __init__(self, comm: NVLinkCommunicator, gather_engine: str = "sm") -> None:
-        """``gather_engine``: how parameter slices are all-gathered (see ``NVLinkCommunicator.all_gather_``)."""
+    def __init__(self, comm: NVLinkCommunicator, gather_engine: str = "sm", reduce_engine: str = "sm") -> None:
+        """``gather_engine`` / ``reduce_engine``: who moves the data of the all-gather and of the
+        reduce-scatter, ``"sm"`` kernels or the ``"copy"`` engines (see ``NVLinkCommunicator.all_gather_``
+        and ``reduce_scatter_``)."""
         self.comm = comm
         self.gather_engine = gather_engine
+        self.reduce_engine = reduce_engine
 
     @property
     def rank(self) -> int:
@@ -721,7 +775,9 @@ class NVLinkShardComm:
         return self.comm.world
 
     def reduce_scatter_(self, full: torch.Tensor, shard_numel: int) -> None:
-        self.comm.reduce_scatter_(full, 1.0)
+        # no closing barrier: the engine votes on the step only after every rank's collectives are done,
+        # and gradients are not written again before that vote
+        self.comm.reduce_scatter_(full, 1.0, self.reduce_engine, closing=False)
 
     def all_gather_(self, full: torch.Tensor, shard_numel: int) -> None:
         self.comm.all_gather_(full, self.gather_engine)

@@ -68,10 +68,14 @@ def _describe(obj: Any, heap: SymmetricHeap) -> Any:
 
 
 class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
-    def __init__(self, heap: SymmetricHeap, timeout: timedelta, max_blocks: int = 128) -> None:
+    def __init__(self, heap: SymmetricHeap, timeout: timedelta, max_blocks: int = 128,
+                 copy_engine_min_bytes: int = 1 << 20) -> None:
+        """``copy_engine_min_bytes``: tensors of at least this size are pulled by a copy engine
+        (``cudaMemcpyAsync`` out of the peer's mapped heap), smaller ones by ``pull_copy_kernel``."""
         self._heap = heap
         self._timeout = timeout
         self._max_blocks = max_blocks
+        self.copy_engine_min_bytes = copy_engine_min_bytes
         self._checkpoint_lock = threading.Lock()
         self._disallowed = False
         self._step = -1
@@ -204,6 +208,15 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
             lib.tft_p2p_pull.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p]
             lib.tft_p2p_pull.restype = ctypes.c_int
             lib.tft_p2p_pull._tft_ready = True  # type: ignore[attr-defined]
+        if nbytes >= self.copy_engine_min_bytes:
+            # big tensors go through a copy engine: link rate, no SM involved
+            if not hasattr(lib.tft_p2p_pull_ce, "_tft_ready"):
+                lib.tft_p2p_pull_ce.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+                lib.tft_p2p_pull_ce.restype = ctypes.c_int
+                lib.tft_p2p_pull_ce._tft_ready = True  # type: ignore[attr-defined]
+            _lib.check(lib.tft_p2p_pull_ce(dst.data_ptr(), src_ptr, nbytes, self._stream.cuda_stream), "tft_p2p_pull_ce")
+            self.bytes_pulled += nbytes
+            return
         main = nbytes // 16 * 16
         if main and dst.data_ptr() % 16 == 0 and src_ptr % 16 == 0:
             _lib.check(lib.tft_p2p_pull(dst.data_ptr(), src_ptr, main, self._max_blocks, self._stream.cuda_stream), "tft_p2p_pull")
