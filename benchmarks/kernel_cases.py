@@ -84,6 +84,18 @@ def case_attention():
     fl = 4.0 * S * S * D * Hq / 2
     report("attn_fwd_kernel<128> (causal)", timeit(lambda: attention_fwd(q, k, v)), flops=fl)
     report("attention backward (delta + dkdv + dq)", timeit(lambda: attention_bwd(do, q, k, v, o, lse)), flops=2.5 * fl)
+    # The library kernel the reference arm of bench.py runs: F.scaled_dot_product_attention (whatever
+    # backend torch picks on this GPU), same shapes, heads-first layout as it wants them.
+    import torch.nn.functional as F
+
+    qh, kh, vh = (t.transpose(1, 2).contiguous().requires_grad_() for t in (q, k, v))
+    doh = do.transpose(1, 2).contiguous()
+    sdpa = lambda: F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=True)  # noqa: E731
+    with torch.no_grad():
+        report("F.scaled_dot_product_attention forward", timeit(sdpa), flops=fl)
+    out = sdpa()
+    report("F.scaled_dot_product_attention backward", timeit(lambda: torch.autograd.grad(out, (qh, kh, vh), doh, retain_graph=True)),
+           flops=2.5 * fl)
 
 
 def case_adamw():
