@@ -33,7 +33,9 @@ except OSError:
     pass
 
 
-def timeit(fn, iters=5, warmup=2):
+def timeit(fn, iters=20, warmup=10):
+    """Mean CUDA-event time of ``iters`` launches after ``warmup`` (enough of both for the clocks to have
+    left their idle state: a handful of sub-millisecond launches is over before the GPU has ramped up)."""
     for _ in range(warmup):
         fn()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -82,8 +84,14 @@ def case_attention():
     q, k, v, do = bf16(B, S, Hq, D), bf16(B, S, Hkv, D), bf16(B, S, Hkv, D), bf16(B, S, Hq, D)
     o, lse = attention_fwd(q, k, v)
     fl = 4.0 * S * S * D * Hq / 2
-    report("attn_fwd_kernel<128> (causal)", timeit(lambda: attention_fwd(q, k, v)), flops=fl)
-    report("attention backward (delta + dkdv + dq)", timeit(lambda: attention_bwd(do, q, k, v, o, lse)), flops=2.5 * fl)
+    report("attn_fwd_kernel<128> (causal, one query tile per CTA)", timeit(lambda: attention_fwd(q, k, v, impl="single")), flops=fl)
+    report("attn_fwd_pair_kernel<128> (causal, two query tiles per CTA)", timeit(lambda: attention_fwd(q, k, v, impl="pair")), flops=fl)
+    report("attention backward (delta + dkdv + dq), P and dS through shared memory",
+           timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="smem")), flops=2.5 * fl)
+    report("attention backward, dQ kernel with dS in tensor memory, dK/dV through shared memory",
+           timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="tmem-dq")), flops=2.5 * fl)
+    report("attention backward (delta + dkdv + dq), P and dS in tensor memory",
+           timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="tmem")), flops=2.5 * fl)
     # The library kernel the reference arm of bench.py runs: F.scaled_dot_product_attention (whatever
     # backend torch picks on this GPU), same shapes, heads-first layout as it wants them.
     import torch.nn.functional as F

@@ -68,6 +68,55 @@ def test_attention_at_the_benchmark_shape():
     _lib.check_status("attention")
 
 
+@pytest.mark.parametrize("shape", [(1, 128, 1, 1, 128), (1, 256, 2, 1, 128), (2, 512, 4, 2, 128), (1, 384, 4, 1, 64),
+                                   (1, 200, 2, 2, 128), (1, 1024, 8, 2, 128), (1, 4096, 8, 2, 128)])
+def test_forward_kernels_agree_with_fp32(shape):
+    """Both forward kernels (one tile per CTA; two tiles per CTA with P and O in tensor memory) against
+    fp32 PyTorch: output and log-sum-exp.  Odd tile counts, a ragged last tile and head dimension 64 included."""
+    from torchft_b200.ops import _lib
+    from torchft_b200.ops.attention import attention_fwd
+
+    B, S, Hq, Hkv, D = shape
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(B, S, h, D, device="cuda").to(torch.bfloat16) for h in (Hq, Hkv, Hkv))
+    # a few large scores make the running maximum jump late in a row (exercises the rescale of O)
+    q[:, S // 2 :, :, 0] *= 8
+    k[:, S - 64 :, :, 0] *= 8
+    qf, kf, vf = q.float(), k.float(), v.float()
+    qh = qf.permute(0, 2, 1, 3)
+    kh = kf.permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
+    vh = vf.permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
+    s = qh @ kh.transpose(-1, -2) / math.sqrt(D)
+    s = s.masked_fill(~torch.ones(S, S, device="cuda", dtype=torch.bool).tril(), float("-inf"))
+    ro = (s.softmax(-1) @ vh).permute(0, 2, 1, 3)
+    rl = torch.logsumexp(s, -1)
+    for impl in ("single", "pair"):
+        o, lse = attention_fwd(q, k, v, impl=impl)
+        assert rel(o, ro) < 2e-2 and norm_rel(o, ro) < 6e-3, (impl, rel(o, ro), norm_rel(o, ro))
+        assert (lse * math.log(2) - rl).abs().max().item() < 2e-3, impl
+        _lib.check_status("attention")
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 1, 1, 128), (1, 256, 2, 1, 128), (2, 512, 4, 2, 128), (1, 384, 4, 1, 64),
+                                   (1, 200, 2, 2, 128), (1, 1024, 8, 2, 128), (1, 4096, 8, 2, 128)])
+def test_backward_kernels_agree_with_fp32(shape):
+    """Both backward paths (P and dS through shared memory; through tensor memory) against fp32 autograd."""
+    from torchft_b200.ops import _lib
+    from torchft_b200.ops.attention import attention_bwd, attention_fwd
+
+    B, S, Hq, Hkv, D = shape
+    torch.manual_seed(4)
+    q, k, v = (torch.randn(B, S, h, D, device="cuda").to(torch.bfloat16) for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
+    o, lse = attention_fwd(q, k, v)
+    _, _, rq, rk, rv = reference(q, k, v, do)
+    for impl in ("smem", "tmem-dq", "tmem"):
+        dq, dk, dv = attention_bwd(do, q, k, v, o, lse, impl=impl)
+        for name, got, want in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+            assert rel(got, want) < 2e-2 and norm_rel(got, want) < 8e-3, (impl, name, rel(got, want), norm_rel(got, want))
+        _lib.check_status("attention")
+
+
 def test_attention_on_fused_qkv_views():
     from torchft_b200.ops.attention import attention_bwd, attention_fwd
 

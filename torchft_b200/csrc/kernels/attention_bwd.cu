@@ -17,66 +17,6 @@
 namespace tft {
 namespace attn {
 
-// ------------------------------------------------------------------ delta
-template <int HD>
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
-                                  float* __restrict__ delta, int B, int S, int Hq) {
-  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const long long total = static_cast<long long>(B) * S * Hq;
-  if (gw >= total) return;
-  const int h = static_cast<int>(gw % Hq);
-  const long long tok = gw / Hq;
-  const int s = static_cast<int>(tok % S);
-  const int b = static_cast<int>(tok / S);
-  const __nv_bfloat16* o = O + (tok * Hq + h) * HD;
-  const __nv_bfloat16* d = dO + (tok * Hq + h) * HD;
-  float acc = 0.f;
-  for (int i = lane * 2; i < HD; i += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
-    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
-    acc += a.x * c.x + a.y * c.y;
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) delta[(static_cast<long long>(b) * Hq + h) * S + s] = acc;
-}
-
-// Writes 32 consecutive values of row r (columns c*32 .. c*32+31) as bf16 into a swizzled tile.
-__device__ __forceinline__ void store_row_chunk(uint8_t* tile, int r, int c, const float (&v)[32]) {
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    uint4 u;
-    u.x = pack_bf16(v[t * 8 + 0], v[t * 8 + 1]);
-    u.y = pack_bf16(v[t * 8 + 2], v[t * 8 + 3]);
-    u.z = pack_bf16(v[t * 8 + 4], v[t * 8 + 5]);
-    u.w = pack_bf16(v[t * 8 + 6], v[t * 8 + 7]);
-    *reinterpret_cast<uint4*>(tile + swizzled_chunk(r, c * 4 + t)) = u;
-  }
-}
-
-// Drains a [128 x HD] fp32 accumulator from tensor memory into global bf16 rows.
-template <int HD>
-__device__ __forceinline__ void store_acc(uint32_t taddr, __nv_bfloat16* dst, float mul, bool valid) {
-#pragma unroll 1
-  for (int c = 0; c < HD / 32; ++c) {
-    uint32_t a[32];
-    tmem_ld_32x32(taddr + c * 32, a);
-    tmem_ld_wait();
-    if (valid) {
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        uint4 u;
-        u.x = pack_bf16(__uint_as_float(a[t * 8 + 0]) * mul, __uint_as_float(a[t * 8 + 1]) * mul);
-        u.y = pack_bf16(__uint_as_float(a[t * 8 + 2]) * mul, __uint_as_float(a[t * 8 + 3]) * mul);
-        u.z = pack_bf16(__uint_as_float(a[t * 8 + 4]) * mul, __uint_as_float(a[t * 8 + 5]) * mul);
-        u.w = pack_bf16(__uint_as_float(a[t * 8 + 6]) * mul, __uint_as_float(a[t * 8 + 7]) * mul);
-        reinterpret_cast<uint4*>(dst + c * 32)[t] = u;
-      }
-    }
-  }
-}
-
 // ------------------------------------------------------------------ dK, dV
 // Q and dO tiles are double buffered.  P and dS share ONE operand buffer: P is written first
 // and consumed by the dV MMAs, then dS (kept in registers meanwhile) overwrites it for the dK
@@ -474,7 +414,7 @@ template <int HD>
 int launch_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
                float* delta, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv, long long ldq,
                long long ldk, long long ldv, long long lddq, long long lddk, long long lddv, float scale,
-               int* status, cudaStream_t stream) {
+               int* status, cudaStream_t stream, int parts = 7) {
   CUtensorMap tq, tk, tv, tdo;
   if (!make_attn_tensormap(&tq, q, HD, Hq, S, B, ldq)) return -2;
   if (!make_attn_tensormap(&tk, k, HD, Hkv, S, B, ldk)) return -3;
@@ -492,14 +432,17 @@ int launch_bwd(const void* dout, const void* q, const void* k, const void* v, co
   cudaGetLastError();
   const float scale_log2 = scale * 1.4426950408889634f;
   const long long warps = static_cast<long long>(B) * S * Hq;
-  attn_delta_kernel<HD><<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq);
+  if (parts & 1)
+    attn_delta_kernel<HD><<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, S, Hq);
   const int n_tiles = (S + BLK - 1) / BLK;
-  attn_dkdv_kernel<HD><<<dim3(n_tiles * Hkv, B, 1), 320, DkvSmem<HD>::TOTAL, stream>>>(
-      tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), S, Hq, Hkv, lddk,
-      lddv, scale, scale_log2, status);
-  attn_dq_kernel<HD><<<dim3(n_tiles * Hq, B, 1), 320, DqSmem<HD>::TOTAL, stream>>>(
-      tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dq), S, Hq, Hkv, lddq, scale, scale_log2, status);
+  if (parts & 2)
+    attn_dkdv_kernel<HD><<<dim3(n_tiles * Hkv, B, 1), 320, DkvSmem<HD>::TOTAL, stream>>>(
+        tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), S, Hq, Hkv, lddk,
+        lddv, scale, scale_log2, status);
+  if (parts & 4)
+    attn_dq_kernel<HD><<<dim3(n_tiles * Hq, B, 1), 320, DqSmem<HD>::TOTAL, stream>>>(
+        tq, tk, tv, tdo, lse, delta, static_cast<__nv_bfloat16*>(dq), S, Hq, Hkv, lddq, scale, scale_log2, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -521,5 +464,22 @@ TFT_API int tft_attn_bwd(const void* dout, const void* q, const void* k, const v
   if (hd == 64)
     return launch_bwd<64>(dout, q, k, v, o, lse, delta, dq, dk, dv, B, S, Hq, Hkv, ldq, ldk, ldv, lddq, lddk, lddv,
                           scale, status, stream);
+  return -1;
+}
+
+// The same with a choice of kernels: parts = 1 (delta) | 2 (dK/dV) | 4 (dQ).  The kernels of
+// attention_bwd_tmem.cu take the place of the ones left out.
+TFT_API int tft_attn_bwd_parts(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                               const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int Hq,
+                               int Hkv, int hd, int ldq, int ldk, int ldv, int lddq, int lddk, int lddv, float scale,
+                               int* status, cudaStream_t stream, int parts) {
+  using namespace tft::attn;
+  if (Hq % Hkv || (ldq % 8) || (ldk % 8) || (ldv % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8)) return -1;
+  if (hd == 128)
+    return launch_bwd<128>(dout, q, k, v, o, lse, delta, dq, dk, dv, B, S, Hq, Hkv, ldq, ldk, ldv, lddq, lddk, lddv,
+                           scale, status, stream, parts);
+  if (hd == 64)
+    return launch_bwd<64>(dout, q, k, v, o, lse, delta, dq, dk, dv, B, S, Hq, Hkv, ldq, ldk, ldv, lddq, lddk, lddv,
+                          scale, status, stream, parts);
   return -1;
 }

@@ -61,6 +61,66 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// ------------------------------------------------------------------ delta
+template <int HD>
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                  float* __restrict__ delta, int B, int S, int Hq) {
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * Hq;
+  if (gw >= total) return;
+  const int h = static_cast<int>(gw % Hq);
+  const long long tok = gw / Hq;
+  const int s = static_cast<int>(tok % S);
+  const int b = static_cast<int>(tok / S);
+  const __nv_bfloat16* o = O + (tok * Hq + h) * HD;
+  const __nv_bfloat16* d = dO + (tok * Hq + h) * HD;
+  float acc = 0.f;
+  for (int i = lane * 2; i < HD; i += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    acc += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<long long>(b) * Hq + h) * S + s] = acc;
+}
+
+// Writes 32 consecutive values of row r (columns c*32 .. c*32+31) as bf16 into a swizzled tile.
+__device__ __forceinline__ void store_row_chunk(uint8_t* tile, int r, int c, const float (&v)[32]) {
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    uint4 u;
+    u.x = pack_bf16(v[t * 8 + 0], v[t * 8 + 1]);
+    u.y = pack_bf16(v[t * 8 + 2], v[t * 8 + 3]);
+    u.z = pack_bf16(v[t * 8 + 4], v[t * 8 + 5]);
+    u.w = pack_bf16(v[t * 8 + 6], v[t * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + swizzled_chunk(r, c * 4 + t)) = u;
+  }
+}
+
+// Drains a [128 x HD] fp32 accumulator from tensor memory into global bf16 rows.
+template <int HD>
+__device__ __forceinline__ void store_acc(uint32_t taddr, __nv_bfloat16* dst, float mul, bool valid) {
+#pragma unroll 1
+  for (int c = 0; c < HD / 32; ++c) {
+    uint32_t a[32];
+    tmem_ld_32x32(taddr + c * 32, a);
+    tmem_ld_wait();
+    if (valid) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        uint4 u;
+        u.x = pack_bf16(__uint_as_float(a[t * 8 + 0]) * mul, __uint_as_float(a[t * 8 + 1]) * mul);
+        u.y = pack_bf16(__uint_as_float(a[t * 8 + 2]) * mul, __uint_as_float(a[t * 8 + 3]) * mul);
+        u.z = pack_bf16(__uint_as_float(a[t * 8 + 4]) * mul, __uint_as_float(a[t * 8 + 5]) * mul);
+        u.w = pack_bf16(__uint_as_float(a[t * 8 + 6]) * mul, __uint_as_float(a[t * 8 + 7]) * mul);
+        reinterpret_cast<uint4*>(dst + c * 32)[t] = u;
+      }
+    }
+  }
+}
+
 // 4-D tensor map over x[batch, seq, heads, HD] (token stride `ld` elements) with boxes of
 // {64, 1, 128, 1}.
 inline bool make_attn_tensormap(CUtensorMap* out, const void* ptr, int hd, int heads, int seq, int batch,

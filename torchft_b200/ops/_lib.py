@@ -39,7 +39,11 @@ _PROTOTYPES = {
     "tft_pseudograd": [P, P, L, I, P],
     "tft_nesterov_outer": [P, P, P, L, F, F, I, I, I, P],
     "tft_attn_fwd": [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
+    "tft_attn_fwd_pair": [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "tft_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tft_attn_bwd_parts": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I],
+    "tft_attn_dq_tmem": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tft_attn_bwd_tmem": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I],
 }
 
 

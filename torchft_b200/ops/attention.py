@@ -1,9 +1,15 @@
 """Causal grouped-query flash attention on tcgen05 tensor cores
-(``csrc/kernels/attention_fwd.cu`` and ``attention_bwd.cu``)."""
+(``csrc/kernels/attention_fwd_pair.cu``, ``attention_fwd.cu`` and ``attention_bwd.cu``).
+
+Two forward kernels with one contract: ``pair`` runs two query tiles per CTA in ping-pong, keeps P in
+tensor memory and accumulates the output there; ``single`` runs one tile per CTA with P through shared
+memory.  ``TFT_ATTN_FWD`` in the environment picks one for the process, ``impl=`` per call.
+"""
 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -18,14 +24,20 @@ def _token_stride(t: torch.Tensor) -> int:
     return t.stride(1)
 
 
-def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+FWD_IMPL = os.environ.get("TFT_ATTN_FWD", "pair")
+assert FWD_IMPL in ("single", "pair"), f"TFT_ATTN_FWD must be 'single' or 'pair', not {FWD_IMPL!r}"
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+                  impl: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """``q [B,S,Hq,D]``, ``k/v [B,S,Hkv,D]`` (bf16) -> ``(o [B,S,Hq,D], lse [B,Hq,S])``."""
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     o = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
-    code = _lib.lib().tft_attn_fwd(
+    fn = _lib.lib().tft_attn_fwd_pair if (impl or FWD_IMPL) == "pair" else _lib.lib().tft_attn_fwd
+    code = fn(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), B, S, Hq, Hkv, D,
         _token_stride(q), _token_stride(k), _token_stride(v), scale, _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
     )
@@ -34,10 +46,18 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Opti
     return o, lse
 
 
+BWD_IMPL = os.environ.get("TFT_ATTN_BWD", "tmem-dq")
+assert BWD_IMPL in ("smem", "tmem", "tmem-dq"), f"TFT_ATTN_BWD must be 'smem', 'tmem' or 'tmem-dq', not {BWD_IMPL!r}"
+
+
 def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
                   scale: Optional[float] = None,
-                  out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Gradients ``(dq, dk, dv)``; ``out`` may name preallocated (possibly strided) destinations."""
+                  out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+                  impl: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients ``(dq, dk, dv)``; ``out`` may name preallocated (possibly strided) destinations.
+
+    ``impl="smem"``: P and dS go through shared memory (``attention_bwd.cu``); ``"tmem"``: they stay in
+    tensor memory as MMA operands (``attention_bwd_tmem.cu``).  Default from ``TFT_ATTN_BWD``."""
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
@@ -49,13 +69,19 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
         dq, dk, dv = out
     delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
     do = do if do.is_contiguous() else do.contiguous()
-    code = _lib.lib().tft_attn_bwd(
-        _lib.ptr(do), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(delta),
-        _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), B, S, Hq, Hkv, D,
-        _token_stride(q), _token_stride(k), _token_stride(v), _token_stride(dq), _token_stride(dk), _token_stride(dv),
-        scale, _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
-    )
-    _lib.check(code, "tft_attn_bwd")
+    status = _lib.ptr(_lib.status_word(q.device))
+    common = (_lib.ptr(do), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(delta),
+              _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), B, S, Hq, Hkv, D,
+              _token_stride(q), _token_stride(k), _token_stride(v), _token_stride(dq), _token_stride(dk), _token_stride(dv),
+              scale, status, _lib.stream_ptr())
+    which = impl or BWD_IMPL
+    if which == "tmem":
+        _lib.check(_lib.lib().tft_attn_bwd_tmem(*common, 7), "tft_attn_bwd_tmem")
+    elif which == "tmem-dq":  # dQ from tensor memory behind the shared-memory dK/dV kernel
+        _lib.check(_lib.lib().tft_attn_bwd_parts(*common, 3), "tft_attn_bwd_parts")
+        _lib.check(_lib.lib().tft_attn_bwd_tmem(*common, 4), "tft_attn_bwd_tmem")
+    else:
+        _lib.check(_lib.lib().tft_attn_bwd(*common), "tft_attn_bwd")
     _lib.count_launch(3)
     return dq, dk, dv
 
