@@ -8,6 +8,8 @@ its buffer with the others:
 
 * ``nvlink``: one launch of the fused peer-memory kernel (sum + 1/n scaling in the same pass)
   on a buffer in the symmetric heap -- what ``Manager.allreduce`` runs on ``ProcessGroupNVLink``;
+  up to 128 KiB also ``nvlink_oneshot``, the one-block one-shot variant (every rank reduces the whole
+  buffer), which is what the dispatch threshold ``oneshot_max_bytes`` is chosen from;
 * ``nccl``: ``all_reduce(SUM)`` followed by the separate ``div_`` kernel -- what the reference's
   ``Manager.allreduce`` runs on ``ProcessGroupNCCL`` (``torchft/manager.py:274,287``).  NCCL runs
   with whatever ``NCCL_NVLS_ENABLE`` says; the JSON lines record it (unset = NCCL's default, which
@@ -58,6 +60,8 @@ def main() -> None:
     heap = SymmetricHeap.get((args.max_mib << 20) + (64 << 20))
     comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=30), max_blocks=int(os.environ.get("TFT_BLOCKS", 64)))
     comm.configure(PrefixStore("arbench", store), rank, world, 0)
+    oneshot = NVLinkCommunicator(heap, timeout=timedelta(seconds=30), oneshot_max_bytes=128 << 10)
+    oneshot.configure(PrefixStore("arbench1", store), rank, world, 0)
     buf = heap.alloc(args.max_mib << 20, torch.uint8)
     ref = torch.empty(args.max_mib << 20, dtype=torch.uint8, device="cuda")
     nvls = os.environ.get("NCCL_NVLS_ENABLE", "default")
@@ -102,6 +106,7 @@ def main() -> None:
             a.normal_()
             b.copy_(a)
             ours = timed(lambda: comm.allreduce_(a, 1.0 / world), nbytes)
+            one = timed(lambda: oneshot.allreduce_(a, 1.0 / world), nbytes) if nbytes <= (128 << 10) else None
             nccl = None if args.skip_nccl else timed(lambda: (dist.all_reduce(b), b.div_(world)), nbytes)
             comm.check()
             if rank == 0:
@@ -109,6 +114,8 @@ def main() -> None:
                 row = {"dtype": str(dtype).replace("torch.", ""), "bytes": nbytes, "ranks": world,
                        "nvlink_fused_us": round(ours * 1e3, 2), "nvlink_busbw_GBs": round(bus / ours / 1e6, 1),
                        "nccl_nvls": nvls}
+                if one is not None:
+                    row["nvlink_oneshot_us"] = round(one * 1e3, 2)
                 if nccl is not None:
                     row.update({"nccl_plus_div_us": round(nccl * 1e3, 2), "nccl_busbw_GBs": round(bus / nccl / 1e6, 1),
                                 "speedup": round(nccl / ours, 2)})

@@ -83,6 +83,23 @@ def _collectives(rank, world, port):
             ref = sum(v.to(dtype).float() for r, v in enumerate(vals) if r != 0)
             err = (t.float() - ref).abs().max().item()
             assert err < (4e-2 if dtype == torch.bfloat16 else 1e-5), ("contrib", dtype, n, err)
+    # one-shot variant for small buffers (every rank reduces everything; one block)
+    small = NVLinkCommunicator(heap, timeout=timedelta(seconds=20), oneshot_max_bytes=128 << 10)
+    small.configure(PrefixStore("t1os", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)), rank, world, 0)
+    for dtype, n in ((torch.bfloat16, 8), (torch.bfloat16, 65536), (torch.float32, 1000 * 4), (torch.float32, 32768)):
+        t = heap.alloc(n, dtype)
+        vals = [torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7 + r)) for r in range(world)]
+        t.copy_(vals[rank].to(dtype))
+        small.allreduce_(t, 1.0 / world)
+        ref = sum(v.to(dtype).float() for v in vals) / world
+        err = (t.float() - ref).abs().max().item()
+        assert err < (2e-2 if dtype == torch.bfloat16 else 1e-5), ("one-shot", dtype, n, err)
+        t.copy_(vals[rank].to(dtype))
+        small.allreduce_(t, 1.0, contribute=(rank != 0))
+        ref = sum(v.to(dtype).float() for r, v in enumerate(vals) if r != 0)
+        err = (t.float() - ref).abs().max().item()
+        assert err < (4e-2 if dtype == torch.bfloat16 else 1e-5), ("one-shot, muted rank", dtype, n, err)
+    small.check()
     # allreduce with the copy engines moving the data: same result as the kernel to rounding
     big = NVLinkCommunicator(heap, timeout=timedelta(seconds=20), copy_engine_min_bytes=1 << 16)
     big.configure(PrefixStore("t1ce", TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)), rank, world, 0)
@@ -357,6 +374,74 @@ def _shard_peer_skips(rank, world, port):
 def test_shard_peer_missing_fails_the_vote_and_the_group_recovers():
     _need_gpus(2)
     _spawn(_shard_peer_skips, 2)
+
+
+def _ddp_buckets_in_heap(rank, world, port):
+    """torch's DDP reducer allocates its gradient buckets by itself; built under the heap's memory pool they
+    are heap tensors, so the NVLink group reduces them in place (no staging copies), and the averaged
+    gradients match a single process that sees both batches."""
+    from torch import nn
+    from torch.distributed import TCPStore
+
+    from torchft_b200 import _control
+    from torchft_b200.ddp import DistributedDataParallel
+    from torchft_b200.manager import Manager
+    from torchft_b200.optim import OptimizerWrapper
+    from torchft_b200.parallel.nvlink import ProcessGroupNVLink, SymmetricHeap
+
+    _control.set_log_enabled(False)
+    store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
+    lighthouse = None
+    if rank == 0:
+        lighthouse = _control.Lighthouse(bind="[::]:0", min_replicas=world, join_timeout_ms=20000, quorum_tick_ms=10)
+        store.set("lighthouse", lighthouse.address())
+    group_store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+    heap = SymmetricHeap.get(512 << 20)
+    pg = ProcessGroupNVLink(timeout=timedelta(seconds=30), heap=heap, staging_bytes=1 << 20)
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(256, 512), nn.Tanh(), nn.Linear(512, 64)).cuda()
+    reference = nn.Sequential(nn.Linear(256, 512), nn.Tanh(), nn.Linear(512, 64)).cuda()
+    reference.load_state_dict(model.state_dict())
+    manager = Manager(
+        pg=pg, load_state_dict=lambda sd: model.load_state_dict(sd), state_dict=lambda: model.state_dict(),
+        min_replica_size=world, timeout=timedelta(seconds=30), quorum_timeout=timedelta(seconds=30), rank=0, world_size=1,
+        store_addr="127.0.0.1", store_port=group_store.port, lighthouse_addr=store.get("lighthouse").decode(),
+        replica_id=f"ddp_{rank}_", hostname="127.0.0.1",
+    )
+    seen = []
+    real = pg.allreduce_scaled
+
+    def spy(tensor, scale, contribute=True):
+        seen.append(heap.offset_of(tensor) is not None)
+        return real(tensor, scale, contribute)
+
+    pg.allreduce_scaled = spy
+    with heap.allocating(64 << 20):
+        ddp = DistributedDataParallel(manager, model, gradient_as_bucket_view=True, bucket_cap_mb=1)
+    optimizer = OptimizerWrapper(manager, torch.optim.SGD(model.parameters(), lr=0.0))
+    batches = [torch.randn(8, 256, generator=torch.Generator().manual_seed(40 + r)).cuda() for r in range(world)]
+    for step in (1, 2):  # step 1 is the initial weight sync; from step 2 on both replicas count
+        optimizer.zero_grad()
+        ddp(batches[rank]).pow(2).mean().backward()
+        optimizer.step()
+        assert manager.errored() is None and manager.current_step() == step
+    assert seen and all(seen), f"buckets outside the heap: {seen}"
+    sum(reference(b).pow(2).mean() for b in batches).div(world).backward()
+    for p, p_ref in zip(model.parameters(), reference.parameters()):
+        err = (p.grad - p_ref.grad).abs().max().item() / max(p_ref.grad.abs().max().item(), 1e-12)
+        assert err < 1e-5, err
+    store.set(f"done/{rank}", b"1")
+    for r in range(world):
+        store.get(f"done/{r}")
+    manager.shutdown(wait=False)
+    if lighthouse is not None:
+        lighthouse.shutdown()
+    return "ok"
+
+
+def test_ddp_gradient_buckets_live_in_the_heap():
+    _need_gpus(2)
+    _spawn(_ddp_buckets_in_heap, 2)
 
 
 def _hsdp_shards(rank, world, port):

@@ -20,6 +20,9 @@
 // watches a host-mapped abort word; on expiry the kernel records a status and returns.
 #include "p2p_common.cuh"
 
+#include <cstdio>
+#include <mutex>
+
 namespace tft {
 namespace p2p {
 
@@ -124,6 +127,45 @@ allreduce_kernel(Comm c, size_t off, long long nvec, float scale, int contribute
     }
   }
   finish(c, flag);
+}
+
+// One-shot allreduce for buffers of at most ONE_SHOT_MAX_VEC vectors, in ONE block: every rank loads
+// the whole buffer from every contributing peer, keeps its sums in registers across the end
+// hand-shake (nobody may overwrite its buffer before all peers have read it) and then writes its own
+// copy.  Against the two-shot kernel it saves the remote stores, the system-wide fence behind them
+// and the inter-block counter; it moves world - 1 times the buffer instead of 2 (world - 1) / world.
+constexpr int ONE_SHOT_THREADS = 1024, ONE_SHOT_VPT = 8;
+constexpr long long ONE_SHOT_MAX_VEC = static_cast<long long>(ONE_SHOT_THREADS) * ONE_SHOT_VPT;  // 128 KiB
+template <typename T>
+__global__ void __launch_bounds__(ONE_SHOT_THREADS)
+allreduce_oneshot_kernel(Comm c, size_t off, long long nvec, float scale, int contribute) {
+  __shared__ int flag[2];
+  signal_pad(c, START_PAD, c.seq, contribute);
+  uint32_t mask = 0;
+  if (!wait_pad(c, START_PAD, c.seq, &mask, flag)) return;
+  uint4 out[ONE_SHOT_VPT];
+#pragma unroll
+  for (int u = 0; u < ONE_SHOT_VPT; ++u) {
+    const long long i = threadIdx.x + static_cast<long long>(u) * ONE_SHOT_THREADS;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (i < nvec) {
+#pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k >= c.world) break;
+        const int p = (c.rank + k) % c.world;
+        if (mask & (1u << p)) Vec<T>::add(acc, ld_peer_v4(c.heap[p] + off + i * 16));
+      }
+    }
+    out[u] = Vec<T>::pack(acc, scale);
+  }
+  __syncthreads();  // every thread of this rank holds its sums: tell the peers, wait for theirs
+  signal_pad(c, END_PAD, c.seq, 0);
+  if (!wait_pad(c, END_PAD, c.seq, nullptr, flag)) return;
+#pragma unroll
+  for (int u = 0; u < ONE_SHOT_VPT; ++u) {
+    const long long i = threadIdx.x + static_cast<long long>(u) * ONE_SHOT_THREADS;
+    if (i < nvec) *reinterpret_cast<uint4*>(c.heap[c.rank] + off + i * 16) = out[u];
+  }
 }
 
 // Slice r = vectors [r*slice_vec, (r+1)*slice_vec) of the buffer at `off`.
@@ -481,6 +523,22 @@ TFT_API int tft_p2p_allreduce(void* const* heaps, int rank, int world, unsigned 
   return static_cast<int>(cudaGetLastError());
 }
 
+// The one-shot variant; bytes <= tft_p2p_allreduce_oneshot_max().  Every member must pick the same variant.
+TFT_API long long tft_p2p_allreduce_oneshot_max() { return ONE_SHOT_MAX_VEC * 16; }
+TFT_API int tft_p2p_allreduce_oneshot(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq,
+                                      int timeout_ms, const int* abort_word, int* status, long long off, long long bytes,
+                                      int dtype, float scale, int contribute, cudaStream_t stream) {
+  if ((off | bytes) & 15) return -1;
+  if (bytes > ONE_SHOT_MAX_VEC * 16) return -6;
+  Comm c = make_comm(heaps, rank, world, epoch, seq, timeout_ms, abort_word, status);
+  const long long nvec = bytes / 16;
+  if (dtype == 0)
+    allreduce_oneshot_kernel<__nv_bfloat16><<<1, ONE_SHOT_THREADS, 0, stream>>>(c, static_cast<size_t>(off), nvec, scale, contribute);
+  else
+    allreduce_oneshot_kernel<float><<<1, ONE_SHOT_THREADS, 0, stream>>>(c, static_cast<size_t>(off), nvec, scale, contribute);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // The buffer holds `world` slices of slice_bytes each; rank r ends with the scaled sum in slice r.
 TFT_API int tft_p2p_reduce_scatter(void* const* heaps, int rank, int world, unsigned epoch, unsigned seq,
                                    int timeout_ms, const int* abort_word, int* status, long long off,
@@ -721,3 +779,46 @@ TFT_API int tft_diloco_outer(void* const* heaps, int rank, int world, unsigned e
   e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(512), params, 0, stream);
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------
+// A slice of the symmetric heap as the backing store of a torch.cuda.MemPool, so that tensors which
+// a library allocates by itself (the gradient buckets of torch's DistributedDataParallel) come to
+// lie inside the heap and the peer-memory collectives can work on them in place.  torch's caching
+// allocator asks for whole segments and keeps them, so a bump pointer is enough; released segments
+// are not reused (the pool is meant to be filled once, at set-up).
+namespace {
+struct PoolRegion {
+  uint8_t* base;
+  size_t bytes, cursor;
+};
+PoolRegion g_pool[64] = {};
+std::mutex g_pool_mu;
+}  // namespace
+
+TFT_API int tft_pool_bind(int device, void* base, long long bytes) {
+  if (device < 0 || device >= 64 || bytes < 0 || (reinterpret_cast<uintptr_t>(base) & 511)) return -1;
+  std::lock_guard<std::mutex> g(g_pool_mu);
+  g_pool[device] = PoolRegion{static_cast<uint8_t*>(base), static_cast<size_t>(bytes), 0};
+  return 0;
+}
+TFT_API long long tft_pool_used(int device) {
+  if (device < 0 || device >= 64) return -1;
+  std::lock_guard<std::mutex> g(g_pool_mu);
+  return static_cast<long long>(g_pool[device].cursor);
+}
+// Signatures of torch.cuda.memory.CUDAPluggableAllocator.  A null result makes torch report out-of-memory.
+TFT_API void* tft_pool_malloc(ssize_t size, int device, cudaStream_t) {
+  if (device < 0 || device >= 64 || size < 0) return nullptr;
+  std::lock_guard<std::mutex> g(g_pool_mu);
+  PoolRegion& r = g_pool[device];
+  const size_t need = (static_cast<size_t>(size) + 511) & ~static_cast<size_t>(511);
+  if (r.base == nullptr || r.cursor + need > r.bytes) {
+    std::fprintf(stderr, "torchft_b200: heap pool of device %d exhausted (%zu of %zu bytes used, %zu asked)\n", device,
+                 r.cursor, r.bytes, need);
+    return nullptr;
+  }
+  void* p = r.base + r.cursor;
+  r.cursor += need;
+  return p;
+}
+TFT_API void tft_pool_free(void*, size_t, int, cudaStream_t) {}

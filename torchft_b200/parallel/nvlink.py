@@ -64,6 +64,7 @@ def _lib_p2p() -> ctypes.CDLL:
             "tft_p2p_all_gather_ce": head + [L, L, I, P],
             "tft_p2p_reduce_scatter_ce": head + [L, L, I, F, P, I, I, P],
             "tft_p2p_allreduce_ce": head + [L, L, I, F, P, I, P],
+            "tft_p2p_allreduce_oneshot": head + [L, L, I, F, I, P],
             "tft_p2p_broadcast": head + [L, L, I, I, P],
             "tft_p2p_barrier": head + [P],
             "tft_ag_gemm_bf16": head + [P, L, P, I, I, I, I, I, P, I, P],
@@ -102,6 +103,8 @@ class SymmetricHeap:
         self.handle = bytes(handle)
         self._bytes = torch.as_tensor(_RawCudaBuffer(self.ptr, self.nbytes), device=self.device)
         self._cursor = self.header_bytes
+        self._pool = None
+        self._pool_allocator = None
         self._channels = 0
         self._lock = threading.Lock()
 
@@ -137,6 +140,33 @@ class SymmetricHeap:
                 )
             self._cursor = start + nbytes
         return self._bytes[start : start + nbytes].view(dtype)
+
+    def mem_pool(self, nbytes: int) -> "torch.cuda.MemPool":
+        """A ``torch.cuda.MemPool`` whose memory is a slice of ``nbytes`` of this heap.
+
+        Tensors allocated under ``torch.cuda.use_mem_pool(pool)`` -- by anyone, including libraries that
+        allocate for themselves -- then lie inside the heap.  Meant for set-up time: wrap a model in
+        ``DistributedDataParallel`` under it and its gradient buckets are heap tensors, which
+        ``ProcessGroupNVLink`` reduces in place instead of staging them.  Every rank must make the same
+        allocations in the same order (the collectives address peers by offset).  One pool per heap.
+        """
+        if self._pool is None:
+            from torchft_b200.utils import build
+
+            lib = _lib_p2p()
+            region = self.alloc(nbytes + 512, torch.uint8)
+            start = (region.data_ptr() + 511) // 512 * 512
+            lib.tft_pool_bind.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64]
+            lib.tft_pool_bind.restype = ctypes.c_int
+            _lib.check(lib.tft_pool_bind(self.device.index or 0, start, nbytes), "tft_pool_bind")
+            allocator = torch.cuda.memory.CUDAPluggableAllocator(str(build.kernels_lib_path()), "tft_pool_malloc", "tft_pool_free")
+            self._pool_allocator = allocator  # must outlive the pool
+            self._pool = torch.cuda.MemPool(allocator.allocator())
+        return self._pool
+
+    def allocating(self, nbytes: int):
+        """Context manager: CUDA allocations of this thread on this device come from the heap (see ``mem_pool``)."""
+        return torch.cuda.use_mem_pool(self.mem_pool(nbytes), device=self.device)
 
     def offset_of(self, t: torch.Tensor) -> Optional[int]:
         """Byte offset of ``t`` inside the heap, or None if it lives elsewhere."""
@@ -215,9 +245,11 @@ class _StreamWork(dist._Work):
 
 class NVLinkCommunicator:
     def __init__(self, heap: SymmetricHeap, timeout: timedelta = timedelta(seconds=10), max_blocks: int = 64,
-                 copy_engine_min_bytes: Optional[int] = None) -> None:
+                 copy_engine_min_bytes: Optional[int] = None, oneshot_max_bytes: int = 0) -> None:
         """
         Args:
+            oneshot_max_bytes: allreduce buffers up to this size (at most 128 KiB) use the one-block
+                one-shot kernel instead of the two-shot one (0: never).  Every member must use the same value.
             timeout: budget of every device-side wait (a peer that does not show up within it
                 makes the collective fail with a status instead of hanging)
             max_blocks: thread blocks per collective kernel (SMs lent to communication)
@@ -225,6 +257,7 @@ class NVLinkCommunicator:
                 (see ``allreduce_``); ``None`` keeps every size on the fused kernel
         """
         self.copy_engine_min_bytes = copy_engine_min_bytes
+        self.oneshot_max_bytes = min(int(oneshot_max_bytes), 128 << 10)
         self.heap = heap
         self.device = heap.device
         self.channel = heap.new_channel()
@@ -394,6 +427,12 @@ class NVLinkCommunicator:
         assert nbytes % 16 == 0, "buffer length must be a multiple of 16 bytes"
         dtype = 0 if t.dtype == torch.bfloat16 else 1
         assert t.dtype in (torch.bfloat16, torch.float32)
+        if nbytes <= self.oneshot_max_bytes:
+            code = _lib_p2p().tft_p2p_allreduce_oneshot(*self._head(), self._offset(t), nbytes, dtype, scale,
+                                                        1 if contribute else 0, _lib.stream_ptr())
+            _lib.check(code, "tft_p2p_allreduce_oneshot")
+            _lib.count_launch()
+            return
         if self.copy_engine_min_bytes is not None and nbytes >= self.copy_engine_min_bytes:
             if not contribute:
                 t.zero_()  # rare (a healing replica): costs one pass over the buffer instead of a kernel variant
