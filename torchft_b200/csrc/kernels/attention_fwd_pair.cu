@@ -50,7 +50,7 @@ struct PairSmem {
 
 enum PairBar {
   PQ_FULL = 0, PK_FULL0, PK_FULL1, PV_FULL0, PV_FULL1, PK_EMPTY0, PK_EMPTY1, PV_EMPTY0, PV_EMPTY1,
-  PS_FULL_A, PS_FULL_B, PP_READY_A, PP_READY_B, PO_FULL_A, PO_FULL_B, NUM_PAIR_BARS
+  PS_FULL_A, PS_FULL_B, PP_LO_A, PP_LO_B, PP_HI_A, PP_HI_B, PO_FULL_A, PO_FULL_B, NUM_PAIR_BARS
 };
 
 constexpr int PAIR_THREADS = 320;  // TMA warp, MMA warp, 4 softmax warps per tile
@@ -64,16 +64,28 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
   tmem_st_32x16(taddr + 16, hi);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Maximum of 32 score columns [col0, col0 + 32) of row r; MASKED applies the causal condition col <= r.
+// Four independent chains of three-input maxima: 16 instructions, dependent depth 5.
 template <bool MASKED>
 __device__ __forceinline__ float chunk_row_max(const uint32_t (&sv)[32], int col0, int r) {
-  float a = -INFINITY, b = -INFINITY;
+  float acc[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    if (!MASKED || (col0 + i) <= r) a = fmaxf(a, __uint_as_float(sv[i]));
-    if (!MASKED || (col0 + i + 1) <= r) b = fmaxf(b, __uint_as_float(sv[i + 1]));
+  for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int i0 = i + 2 * c, i1 = i0 + 1;
+      const float a = (!MASKED || (col0 + i0) <= r) ? __uint_as_float(sv[i0]) : -INFINITY;
+      const float b = (!MASKED || (col0 + i1) <= r) ? __uint_as_float(sv[i1]) : -INFINITY;
+      acc[c] = max3(acc[c], a, b);
+    }
   }
-  return fmaxf(a, b);
+  return max3(fmaxf(acc[0], acc[1]), acc[2], acc[3]);
 }
 
 // 2^x on the FMA and integer pipes: x = n + f with n the nearest integer and f in [-0.5, 0.5]; 2^f from a
@@ -146,7 +158,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   const int n_steps = has_b ? n_b : n_a;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_PAIR_BARS; ++i) mbar_init(bar(i), (i == PP_READY_A || i == PP_READY_B) ? 128 : 1);
+    for (int i = 0; i < NUM_PAIR_BARS; ++i) mbar_init(bar(i), (i >= PP_LO_A && i <= PP_HI_B) ? 128 : 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq);
@@ -193,12 +205,25 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
                     idesc_s, k != 0);
         umma_commit(bar(PS_FULL_A + t));
       };
-      auto issue_pv = [&](int t, int j) {
+      // the PV product over keys [64 half, 64 half + 64) of the tile: 16 keys per step = 8 packed columns of P
+      auto issue_pv = [&](int t, int j, int half) {
         const int st = j & 1;
 #pragma unroll
-        for (int k = 0; k < BLK / 16; ++k)  // 16 keys per step = 8 packed columns of P
+        for (int kk = 0; kk < BLK / 32; ++kk) {
+          const int k = half * (BLK / 32) + kk;
           umma_bf16_ts(tmem_o(t), tmem_s(t) + k * 8, mnmajor_desc(base + L::V + st * L::TILE, k), idesc_pv,
                        (j > 0 || k > 0) ? 1u : 0u);
+        }
+      };
+      // P of the first 64 keys is ready before the exponentials of the last 64 are: start on it
+      auto wait_issue_pv = [&](int t, int j) {
+        if (!mbar_wait(bar(PP_LO_A + t), j & 1, abort_flag)) return false;
+        tc_fence_after();
+        issue_pv(t, j, 0);
+        if (!mbar_wait(bar(PP_HI_A + t), j & 1, abort_flag)) return false;
+        tc_fence_after();
+        issue_pv(t, j, 1);
+        return true;
       };
       bool ok = mbar_wait(bar(PQ_FULL), 0, abort_flag) && mbar_wait(bar(PK_FULL0), 0, abort_flag);
       if (ok) {
@@ -211,9 +236,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         const int st = j & 1;
         if (!mbar_wait(bar(PV_FULL0 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
         if (j < n_a) {
-          if (!mbar_wait(bar(PP_READY_A), j & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, j);
+          if (!wait_issue_pv(0, j)) { ok = false; break; }
           if (j == n_a - 1) umma_commit(bar(PO_FULL_A));
         }
         const bool have_next = j + 1 < n_steps;
@@ -223,9 +246,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         }
         if (j + 1 < n_a) issue_s(0, j + 1);
         if (j < n_b) {
-          if (!mbar_wait(bar(PP_READY_B), j & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(1, j);
+          if (!wait_issue_pv(1, j)) { ok = false; break; }
           if (j == n_b - 1) umma_commit(bar(PO_FULL_B));
         }
         umma_commit(bar(PV_EMPTY0 + st));
@@ -291,18 +312,24 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       if (diag) {
         part[0] = chunk_softmax<true>(s0, 0, r, scale_log2, m, s_addr);
         part[1] = chunk_softmax<true>(s1, 1, r, scale_log2, m, s_addr);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(PP_LO_A + t));
         part[2] = chunk_softmax<true>(s2, 2, r, scale_log2, m, s_addr);
         part[3] = chunk_softmax<true>(s3, 3, r, scale_log2, m, s_addr);
       } else {
         part[0] = chunk_softmax<false>(s0, 0, r, scale_log2, m, s_addr);
         part[1] = chunk_softmax<false>(s1, 1, r, scale_log2, m, s_addr);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(PP_LO_A + t));
         part[2] = chunk_softmax<false>(s2, 2, r, scale_log2, m, s_addr);
         part[3] = chunk_softmax<false>(s3, 3, r, scale_log2, m, s_addr);
       }
       l += (part[0] + part[1]) + (part[2] + part[3]);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(PP_READY_A + t));
+      mbar_arrive(bar(PP_HI_A + t));
     }
     if (ok && n_kv > 0) {
       const bool got = mbar_wait(bar(PO_FULL_A + t), 0, abort_flag);
