@@ -53,7 +53,7 @@ def worker(args: argparse.Namespace) -> None:
     _control.set_log_enabled(False)
     torch.cuda.set_device(args.rank)
     cfg = {"llama3_8b": LlamaConfig.llama3_8b, "llama_1b": LlamaConfig.llama_1b, "tiny": LlamaConfig.tiny}[args.model]()
-    seq = cfg.max_seq_len
+    seq = args.seq or cfg.max_seq_len
     n = cfg.num_params() + 64 * 1024 * (cfg.n_layers + 2)
     heap = SymmetricHeap.get(2 * 2 * n + 2 * 4 * (n + 1024) + (1 << 30))
     group_store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
@@ -137,7 +137,7 @@ def parent(args: argparse.Namespace) -> None:
                                      heartbeat_timeout_ms=args.heartbeat_timeout_ms)
     base = [sys.executable, os.path.abspath(__file__), "--worker", "--lighthouse", lighthouse.address(), "--transport",
             args.transport, "--model", args.model, "--steps", str(args.steps), "--kill-at", str(args.kill_at),
-            "--timeout", str(args.timeout), "--device-timeout", str(args.device_timeout)]
+            "--timeout", str(args.timeout), "--device-timeout", str(args.device_timeout), "--seq", str(args.seq)]
 
     def start(rank: int, kill_at: int, restarted: bool) -> subprocess.Popen:
         cmd = [a for a in base]
@@ -190,6 +190,7 @@ def main() -> None:
     ap.add_argument("--lighthouse", default="")
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "http"])
     ap.add_argument("--model", default="llama_1b", choices=["llama3_8b", "llama_1b", "tiny"])
+    ap.add_argument("--seq", type=int, default=0, help="tokens per step and replica (0: the model's maximum)")
     ap.add_argument("--steps", type=int, default=600)
     ap.add_argument("--kill-at", type=int, default=40, help="replica 1 leaves after this many committed steps (0: never)")
     ap.add_argument("--kills", type=int, default=1, help="how many times the replica leaves (every --kill-at steps)")

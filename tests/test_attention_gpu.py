@@ -80,8 +80,10 @@ def test_forward_kernels_agree_with_fp32(shape):
     torch.manual_seed(3)
     q, k, v = (torch.randn(B, S, h, D, device="cuda").to(torch.bfloat16) for h in (Hq, Hkv, Hkv))
     # a few large scores make the running maximum jump late in a row (exercises the rescale of O)
+    # (late keys: the last, masked tile; keys at a quarter of the sequence: a tile in the middle of the rows below)
     q[:, S // 2 :, :, 0] *= 8
     k[:, S - 64 :, :, 0] *= 8
+    k[:, S // 4 : S // 4 + 32, :, 0] *= 8
     qf, kf, vf = q.float(), k.float(), v.float()
     qh = qf.permute(0, 2, 1, 3)
     kh = kf.permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
