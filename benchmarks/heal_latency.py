@@ -45,6 +45,7 @@ def worker(args: argparse.Namespace) -> None:
     from torchft_b200.checkpointing import CheckpointServer
     from torchft_b200.manager import Manager
     from torchft_b200.models.llama import Llama, LlamaConfig
+    from torchft_b200.ops._lib import KernelError
     from torchft_b200.parallel.hsdp import HSDPEngine
     from torchft_b200.parallel.nvlink import ProcessGroupNVLink, SymmetricHeap
     from torchft_b200.parallel.nvlink_heal import NVLinkCheckpointTransport
@@ -55,7 +56,17 @@ def worker(args: argparse.Namespace) -> None:
     cfg = {"llama3_8b": LlamaConfig.llama3_8b, "llama_1b": LlamaConfig.llama_1b, "tiny": LlamaConfig.tiny}[args.model]()
     seq = args.seq or cfg.max_seq_len
     n = cfg.num_params() + 64 * 1024 * (cfg.n_layers + 2)
-    heap = SymmetricHeap.get(2 * 2 * n + 2 * 4 * (n + 1024) + (1 << 30))
+    heap_bytes = 2 * 2 * n + 2 * 4 * (n + 1024) + (1 << 30)
+    for attempt in range(60):
+        # The memory of the process this one replaces is released once the survivors have moved to
+        # a membership without it (they unmap its heap then); until that quorum, allocation can fail.
+        try:
+            heap = SymmetricHeap.get(heap_bytes)
+            break
+        except KernelError:
+            if not args.restarted or attempt == 59:
+                raise
+            time.sleep(0.5)
     group_store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
     model = Llama(cfg, device="cuda")
     model.init_weights(seed=7 + args.rank + (100 if args.restarted else 0))

@@ -206,7 +206,7 @@ def _peer_absent(rank, world, port):
 
     from torch.distributed import ReduceOp, TCPStore
 
-    from torchft_b200.parallel.nvlink import ProcessGroupNVLink
+    from torchft_b200.parallel.nvlink import ProcessGroupNVLink, _PeerMappings
 
     store = TCPStore("127.0.0.1", port, is_master=False, wait_for_workers=False)
     pg = ProcessGroupNVLink(timeout=timedelta(seconds=1))
@@ -224,7 +224,10 @@ def _peer_absent(rank, world, port):
         assert time.time() - t0 < 10
         store.set("rank0_done", b"1")
         # the context is still healthy: reconfigure alone and keep going
+        assert _PeerMappings.open_count() == 1
         pg.configure(f"127.0.0.1:{port}/absent/2", 0, 1)
+        # the peer that left is unmapped: its GPU memory is not pinned by this process any more
+        assert _PeerMappings.open_count() == 0
         t = torch.ones(8, device="cuda")
         pg.allreduce_scaled(t, 0.5).get_future().wait()
         assert torch.all(t == 0.5).item()

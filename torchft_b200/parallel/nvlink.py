@@ -85,6 +85,48 @@ class _RawCudaBuffer:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+class _PeerMappings:
+    """Process-wide table of peer heaps mapped into this process: one CUDA-IPC mapping per handle,
+    reference counted.  A peer's heap stays allocated on ITS GPU for as long as any process keeps it
+    mapped, also after the peer has exited, so a mapping is closed as soon as its last user (a
+    communicator whose membership no longer has the peer, a finished heal transfer) lets go of it:
+    the replacement of a departed replica needs that memory for its own heap."""
+
+    _lock = threading.Lock()
+    _table: Dict[bytes, List[int]] = {}  # handle -> [pointer, references]
+
+    @classmethod
+    def acquire(cls, handle: bytes, device: torch.device) -> int:
+        with cls._lock:
+            entry = cls._table.get(handle)
+            if entry is None:
+                out = ctypes.c_void_p()
+                with torch.cuda.device(device):
+                    _lib.check(_lib_p2p().tft_p2p_peer_open(handle, ctypes.byref(out)), "tft_p2p_peer_open")
+                entry = cls._table[handle] = [int(out.value), 0]
+            entry[1] += 1
+            return entry[0]
+
+    @classmethod
+    def release(cls, handle: bytes, device: torch.device) -> None:
+        """The caller guarantees that nothing it queued on the device still uses the mapping."""
+        with cls._lock:
+            entry = cls._table.get(handle)
+            if entry is None:
+                return
+            entry[1] -= 1
+            if entry[1] > 0:
+                return
+            del cls._table[handle]
+            with torch.cuda.device(device):
+                _lib_p2p().tft_p2p_peer_close(ctypes.c_void_p(entry[0]))
+
+    @classmethod
+    def open_count(cls) -> int:
+        with cls._lock:
+            return len(cls._table)
+
+
 class SymmetricHeap:
     """Device memory that peers can map.  Bump allocator; nothing is ever freed individually."""
 
@@ -267,7 +309,7 @@ class NVLinkCommunicator:
         self.world = 1
         self.epoch = 0
         self.seq = 0
-        self._peers: Dict[bytes, int] = {}  # handle -> mapped pointer (kept open for the process lifetime)
+        self._peers: Dict[bytes, int] = {}  # handle -> mapped pointer, for the peers of the current membership
         self._heaps = (ctypes.c_void_p * MAX_RANKS)()
         self._heaps[0] = heap.ptr
         lib = _lib_p2p()
@@ -333,26 +375,39 @@ class NVLinkCommunicator:
             torch.cuda.synchronize(self.device)
         if world == 1:
             self._heaps[0] = self.heap.ptr
+            self._keep_peers({})
             return
         store.set(f"handle/{rank}", self.heap.handle)
         store.set(f"nbytes/{rank}", str(self.heap.nbytes))
+        peers: Dict[bytes, int] = {}
         for r in range(world):
             if r == rank:
                 self._heaps[r] = self.heap.ptr
                 continue
             handle = bytes(store.get(f"handle/{r}"))
-            ptr = self._peers.get(handle)
+            ptr = self._peers.get(handle) or peers.get(handle)
             if ptr is None:
-                out = ctypes.c_void_p()
-                with torch.cuda.device(self.device):
-                    _lib.check(lib.tft_p2p_peer_open(handle, ctypes.byref(out)), "tft_p2p_peer_open")
-                ptr = int(out.value)
-                self._peers[handle] = ptr
+                ptr = _PeerMappings.acquire(handle, self.device)
+            peers[handle] = ptr
             self._heaps[r] = ptr
+        self._keep_peers(peers)
         # barrier through the store: every header is clean before the first flag is written
         store.set(f"ready/{rank}", b"1")
         for r in range(world):
             store.get(f"ready/{r}")
+
+    def _keep_peers(self, peers: Dict[bytes, int]) -> None:
+        """Lets go of the mappings of peers that left the membership (the device was synchronised at
+        the top of ``configure``: none of this communicator's kernels still reads them)."""
+        for handle in list(self._peers):
+            if handle not in peers:
+                _PeerMappings.release(handle, self.device)
+        self._peers = peers
+
+    def close(self) -> None:
+        """Unmaps every peer (after the device has drained)."""
+        torch.cuda.synchronize(self.device)
+        self._keep_peers({})
 
     def abort(self) -> None:
         """Makes every wait of kernels in flight give up (host-side kill switch)."""

@@ -39,7 +39,7 @@ import torch
 from torchft_b200.checkpointing import CheckpointTransport, _timed_acquire
 from torchft_b200.http import advertised_host, make_http_server
 from torchft_b200.ops import _lib
-from torchft_b200.parallel.nvlink import SymmetricHeap, _lib_p2p, _RawCudaBuffer
+from torchft_b200.parallel.nvlink import SymmetricHeap, _lib_p2p, _PeerMappings, _RawCudaBuffer
 
 logger = logging.getLogger(__name__)
 
@@ -84,7 +84,6 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
         self._ready_event: Optional[torch.cuda.Event] = None
         self._leases_lock = threading.Lock()
         self._targets_fn: Optional[Callable[[], Dict[str, Any]]] = None
-        self._peers: Dict[bytes, int] = {}
         self._stream = torch.cuda.Stream(device=heap.device)
         self._stopped = False
         self.bytes_pulled = 0
@@ -191,16 +190,11 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
         self.allow_checkpoint(step)
 
     def _peer_ptr(self, handle: bytes) -> int:
+        """Maps the sender's heap for one transfer; ``recv_checkpoint`` unmaps it again, so that a
+        sender that later leaves does not keep its memory pinned through this process."""
         if handle == self._heap.handle:
             return self._heap.ptr  # loop-back (tests): a process cannot open its own handle
-        ptr = self._peers.get(handle)
-        if ptr is None:
-            out = ctypes.c_void_p()
-            with torch.cuda.device(self._heap.device):
-                _lib.check(_lib_p2p().tft_p2p_peer_open(handle, ctypes.byref(out)), "tft_p2p_peer_open")
-            ptr = int(out.value)
-            self._peers[handle] = ptr
-        return ptr
+        return _PeerMappings.acquire(handle, self._heap.device)
 
     def _pull(self, dst: torch.Tensor, src_ptr: int, nbytes: int) -> None:
         lib = _lib_p2p()
@@ -251,13 +245,18 @@ class NVLinkCheckpointTransport(CheckpointTransport[Dict[str, Any]]):
     def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> Dict[str, Any]:
         with urllib.request.urlopen(f"{metadata}{step}", timeout=timeout.total_seconds()) as f:
             manifest = pickle.loads(f.read())
+        mapped = False
         try:
             base = self._peer_ptr(manifest["handle"])
+            mapped = manifest["handle"] != self._heap.handle
             targets = self._targets_fn() if self._targets_fn is not None else None
             with torch.cuda.device(self._heap.device), torch.cuda.stream(self._stream):
                 state = self._materialise(manifest["state"], targets, base)
             self._stream.synchronize()
         finally:
+            if mapped:
+                self._stream.synchronize()  # also on the error path: nothing queued may outlive the mapping
+                _PeerMappings.release(manifest["handle"], self._heap.device)
             done_url = metadata.rsplit("/checkpoint/", 1)[0] + f"/done/{manifest['lease']}"
             try:
                 urllib.request.urlopen(done_url, timeout=timeout.total_seconds()).read()
