@@ -35,8 +35,8 @@ class RecordingPG(ProcessGroupDummy):
             raise self.fail_allreduce
         if self.fail_future is not None:
             w = _DummyWork(tensors)
-            w.future_ = torch.futures.Future()
-            w.future_.set_exception(self.fail_future)
+            w._done = torch.futures.Future()
+            w._done.set_exception(self.fail_future)
             return w
         return super().allreduce(tensors, opts)
 

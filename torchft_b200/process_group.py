@@ -289,61 +289,64 @@ class ProcessGroupNCCL(ProcessGroupWrapper):
 
 
 class _DummyWork(dist._Work):
-    """A work item that is already complete."""
+    """A work item that was complete before it was handed out; counts how it is awaited."""
 
-    def __init__(self, result: object) -> None:
+    def __init__(self, result: object, owner: Optional["ProcessGroupDummy"] = None) -> None:
         super().__init__()
-        self.result_ = result
-        self.future_: Future = Future()
-        self.future_.set_result(result)
+        self._owner = owner
+        self._done: Future = Future()
+        self._done.set_result(result)
 
     def wait(self, timeout: Optional[timedelta] = None) -> bool:
+        if self._owner is not None:
+            self._owner.wait_count += 1
         return True
 
     def get_future(self) -> Future:
-        return self.future_
+        if self._owner is not None:
+            self._owner.get_future_count += 1
+        return self._done
 
 
 class ProcessGroupDummy(ProcessGroup):
-    """World-size-1 group that completes every operation immediately.
+    """A group of exactly one rank in which every collective is the identity and already complete.
 
-    Used to absorb collectives a library insists on issuing (for example the parameter
-    broadcast in the ``DistributedDataParallel`` constructor).
+    It stands in where a library insists on communicating although there is nobody to talk to yet:
+    torch's ``DistributedDataParallel`` broadcasts the parameters in its constructor, which
+    ``torchft_b200.ddp`` runs under this group before the real, reconfigurable group takes over.
+    The counters (``configure_count``, ``wait_count``, ``get_future_count``, ``issued``) let tests
+    see what the library did with it.  Reference: ``torchft/process_group.py`` (ProcessGroupDummy).
     """
 
     def __init__(self, rank: int, world: int) -> None:
+        if (rank, world) != (0, 1):
+            raise ValueError(f"a dummy group has one rank, got rank {rank} of {world}")
         super().__init__(rank, world)
-        assert rank == 0
-        assert world == 1
-        self._rank = rank
-        self._world = world
+        self.configure_count = 0
         self.wait_count = 0
         self.get_future_count = 0
-        self._work: List[Work] = []
-        self.configure_count = 0
+        self.issued = 0
+
+    def _complete(self, result: object) -> Work:
+        self.issued += 1
+        return _DummyWork(result, self)
 
     def configure(self, store_addr: str, rank: int, world_size: int) -> None:
         self.configure_count += 1
 
+    def allreduce(self, tensors: List[torch.Tensor], opts: object) -> Work:
+        return self._complete(tensors)  # a sum over one rank
+
     def broadcast(self, tensor_list: List[torch.Tensor], opts: object) -> Work:
-        res = _DummyWork(tensor_list)
-        self._work.append(res)
-        return res
+        return self._complete(tensor_list)  # the root is the only rank
 
     def allgather(self, output_tensors: List[List[torch.Tensor]], input_tensor: List[torch.Tensor], opts: object = None) -> Work:
-        for o, i in zip(output_tensors[0], input_tensor):
-            o.copy_(i)
-        res = _DummyWork(output_tensors)
-        self._work.append(res)
-        return res
-
-    def allreduce(self, tensors: List[torch.Tensor], opts: object) -> Work:
-        res = _DummyWork(tensors)
-        self._work.append(res)
-        return res
+        for slot, mine in zip(output_tensors[0], input_tensor):
+            slot.copy_(mine)
+        return self._complete(output_tensors)
 
     def size(self) -> int:
-        return self._world
+        return 1
 
     def getBackendName(self) -> str:  # noqa: N802
         return "torchft-dummy"
