@@ -49,6 +49,10 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--seq", type=int, default=0, help="sequence length (default: the model's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end phase")
     ap.add_argument("--topology", default="", help="override the layout, '<replica groups>x<shard GPUs>' (default: 1x1, 2x1, 2x2, 2x4)")
+    ap.add_argument("--ddp", action="store_true",
+                    help="the reference arm's layout through the stock interfaces: N replica groups of one GPU, torch "
+                         "DistributedDataParallel (buckets in the symmetric heap) + OptimizerWrapper + FusedAdamW around "
+                         "the same model, kernels and NVLink process group, instead of HSDPEngine")
     ap.add_argument("--fused-gather", action="store_true",
                     help="shard every projection matrix by rows and gather it inside its first GEMM of the step "
                          "(all-gather fused GEMM) instead of with separate all-gather kernels")
@@ -138,6 +142,46 @@ def free_port() -> int:
     return port
 
 
+class DDPArm:
+    """Trains the model the way a user of the stock interfaces would: ``DistributedDataParallel(manager, model)``
+    whose buckets go through ``Manager.allreduce``, ``OptimizerWrapper`` around ``FusedAdamW``.  Parameters,
+    gradient buckets and moments are allocated under the heap's memory pool, so buckets are reduced in place and
+    a joining replica receives its state straight into the live tensors.  Same ``train_step`` / ``state_dict``
+    surface as ``HSDPEngine``."""
+
+    def __init__(self, make_model, manager, heap, pool_bytes: int, lr: float, betas, eps: float, weight_decay: float,
+                 bucket_cap_mb: int) -> None:
+        from torchft_b200.ddp import DistributedDataParallel
+        from torchft_b200.optim import FusedAdamW, OptimizerWrapper
+
+        with heap.allocating(pool_bytes):
+            self.model = make_model()
+            self.ddp = DistributedDataParallel(manager, self.model, gradient_as_bucket_view=True, bucket_cap_mb=bucket_cap_mb)
+            self.adamw = FusedAdamW(self.model.parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.optimizer = OptimizerWrapper(manager, self.adamw)
+        self.timing = None
+
+    def train_step(self, tokens, targets):
+        self.optimizer.zero_grad()  # quorum for this step
+        loss = self.ddp(tokens, targets)
+        loss.backward()  # buckets are averaged over the replica groups as they fill
+        self.optimizer.step()  # commit vote, then the update
+        return loss.detach()
+
+    def state_dict(self):
+        return {"model": self.model.state_dict(), "optim": self.adamw.state_dict()}
+
+    def load_state_dict(self, sd) -> None:
+        import torch
+
+        with torch.no_grad():
+            mine = self.model.state_dict()
+            for k, v in sd["model"].items():
+                if mine[k].data_ptr() != v.data_ptr():
+                    mine[k].copy_(v)
+        self.adamw.load_state_dict(sd["optim"])
+
+
 def run_ours(args: argparse.Namespace) -> None:
     import torch
     import torch.distributed as dist
@@ -163,6 +207,8 @@ def run_ours(args: argparse.Namespace) -> None:
         n_groups, shard_world = (int(v) for v in args.topology.lower().split("x"))
         if n_groups * shard_world != args.gpus:
             raise SystemExit(f"--topology {args.topology} does not multiply to --gpus {args.gpus}")
+    if args.ddp:
+        n_groups, shard_world = args.gpus, 1
     group, shard_rank = divmod(rank, shard_world)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -201,13 +247,19 @@ def run_ours(args: argparse.Namespace) -> None:
     padded = n_params + 64 * 1024 * (cfg.n_layers + 2)
     # bf16 parameters + bf16 gradients (full) and the fp32 AdamW moments of the owned slices
     heap_bytes = 2 * 2 * padded + 2 * 4 * (padded // shard_world + 1024) + (1 << 30)
+    if args.ddp:
+        heap_bytes += 4 << 30  # allocator granularity of ~300 separate tensors and the staging area
     heap = SymmetricHeap.get(heap_bytes, device)
     shard = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
     client_store = TCPStore("127.0.0.1", store_port, is_master=False, wait_for_workers=False)
     shard.bind(client_store, shard_rank, shard_world, "shard")  # fixed membership; renewed after a failed step
 
-    model = Llama(cfg, device=device)
-    model.init_weights(seed=1234)  # identical on every rank, as after the step-0 heal
+    def make_model():
+        m = Llama(cfg, device=device)
+        m.init_weights(seed=1234)  # identical on every rank, as after the step-0 heal
+        return m
+
+    model = None if args.ddp else make_model()
     pg = ProcessGroupNVLink(timeout=timedelta(seconds=60), heap=heap, staging_bytes=64 << 20,
                             copy_engine_min_bytes=(8 << 20) if args.allreduce_engine == "copy" else None)
     engine_box = {}
@@ -230,6 +282,10 @@ def run_ours(args: argparse.Namespace) -> None:
         checkpoint_transport=NVLinkCheckpointTransport(heap, timeout=timedelta(seconds=120)),
     )
     fused = None
+    if args.ddp:
+        engine = DDPArm(make_model, manager, heap, pool_bytes=2 * 2 * padded + 2 * 4 * padded + (3 << 30), lr=3e-4,
+                        betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, bucket_cap_mb=512)
+        engine_box["engine"] = engine
     if args.fused_gather and shard_world > 1:
         fused = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
         fused.bind(client_store, shard_rank, shard_world, "fused")
@@ -237,11 +293,12 @@ def run_ours(args: argparse.Namespace) -> None:
     if args.fused_rs and shard_world > 1:
         fused_rs = NVLinkCommunicator(heap, timeout=timedelta(seconds=60))
         fused_rs.bind(client_store, shard_rank, shard_world, "fused_rs")
-    engine = HSDPEngine(
-        model, model.units(per_weight=fused is not None or fused_rs is not None), fused_rs_comm=fused_rs, manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine, reduce_engine=args.reduce_engine),
-        lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,
-    )
-    engine_box["engine"] = engine
+    if not args.ddp:
+        engine = HSDPEngine(
+            model, model.units(per_weight=fused is not None or fused_rs is not None), fused_rs_comm=fused_rs, manager=manager, shard_comm=NVLinkShardComm(shard, gather_engine=args.gather_engine, reduce_engine=args.reduce_engine),
+            lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, alloc=heap.alloc, fused_gather_comm=fused,
+        )
+        engine_box["engine"] = engine
 
     # ---- data: synthetic token ids in pinned host memory, a fresh batch every step
     total_steps = args.warmup + 2 * args.steps + 8  # a few spare batches for the optional timing pass
@@ -339,9 +396,11 @@ def run_ours(args: argparse.Namespace) -> None:
                           "tiny": "tiny test model"}[args.model],
                 "global_batch": args.gpus * batch,
                 "seq_len": seq,
-                "parallelism": f"hsdp{n_groups}x{shard_world} (replica groups x shard GPUs)",
+                "parallelism": (f"ddp{n_groups}x1 (torch DistributedDataParallel over replica groups of one GPU, 512 MiB buckets in the symmetric heap)"
+                                if args.ddp else f"hsdp{n_groups}x{shard_world} (replica groups x shard GPUs)"),
                 "optimizer": "fused AdamW lr 3e-4 betas (0.9, 0.95) wd 0.1, fp32 moments",
                 "quorum": "lighthouse quorum + should_commit every step",
+                "engine": "DistributedDataParallel + OptimizerWrapper + FusedAdamW" if args.ddp else "HSDPEngine",
                 "parameter_gather": ("inside the first GEMM of each projection (all-gather fused GEMM)" if fused is not None
                                      else f"per-unit all-gather ({args.gather_engine}) overlapped with forward"),
                 "gradient_reduce_scatter": ("inside the weight-gradient GEMM of every projection matrix" if fused_rs is not None

@@ -314,3 +314,42 @@ def test_pure_ddp_remove_hooks_and_sampler_bounds():
         DistributedSampler(list(range(8)), replica_group=2, num_replica_groups=2, rank=0, num_replicas=2)
     with pytest.raises(ValueError):
         DistributedSampler(list(range(8)), replica_group=0, num_replica_groups=2, rank=2, num_replicas=2)
+
+
+def test_fused_adamw_matches_torch_and_keeps_its_state_tensors():
+    """The plain-arithmetic path (parameters that are not bf16 CUDA tensors) against ``torch.optim.AdamW``;
+    the state dict hands out the live fp32 moments and loading copies into them in place."""
+    from torchft_b200.optim import FusedAdamW
+
+    torch.manual_seed(0)
+    ours = [nn.Parameter(torch.randn(17, 5)), nn.Parameter(torch.randn(33))]
+    theirs = [nn.Parameter(p.detach().clone()) for p in ours]
+    kw = dict(lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    a, b = FusedAdamW(ours, **kw), torch.optim.AdamW(theirs, **kw)
+    assert all(a.state[p]["exp_avg"].dtype == torch.float32 for p in ours)  # allocated before the first step
+    for _ in range(5):
+        for p, q in zip(ours, theirs):
+            g = torch.randn_like(p)
+            p.grad, q.grad = g, g.clone()
+        a.step()
+        b.step()
+    for p, q in zip(ours, theirs):
+        assert torch.allclose(p, q, rtol=1e-5, atol=1e-6)
+        assert torch.allclose(a.state[p]["exp_avg_sq"], b.state[q]["exp_avg_sq"], rtol=1e-5, atol=1e-8)
+
+    fresh = [nn.Parameter(torch.zeros_like(p)) for p in ours]
+    c = FusedAdamW(fresh, **kw)
+    kept = [c.state[p]["exp_avg"] for p in fresh]
+    c.load_state_dict(a.state_dict())
+    assert c.param_groups[0]["step"] == 5 and c.param_groups[0]["betas"] == (0.9, 0.95)
+    for p, q, t in zip(fresh, ours, kept):
+        assert c.state[p]["exp_avg"] is t and torch.equal(t, a.state[q]["exp_avg"])
+    # behind the fault-tolerance wrapper the step is gated by the commit vote
+    manager = create_autospec(Manager)
+    manager.should_commit.return_value = False
+    wrapped = OptimizerWrapper(manager, a)
+    before = ours[0].detach().clone()
+    wrapped.step()
+    assert torch.equal(ours[0], before)
+    with pytest.raises(ValueError):
+        FusedAdamW(ours, lr=-1.0)

@@ -259,6 +259,29 @@ def test_adamw_matches_torch():
     assert rel_err(m, st["exp_avg"]) < 1e-4 and rel_err(v, st["exp_avg_sq"]) < 1e-4
 
 
+def test_fused_adamw_optimizer_on_bf16_parameters():
+    """``FusedAdamW`` (one kernel per bf16 parameter, fp32 moments) against ``torch.optim.AdamW`` on fp32 copies."""
+    from torchft_b200.optim import FusedAdamW
+
+    params = [torch.nn.Parameter(bf16(257, 33)), torch.nn.Parameter(bf16(1000))]
+    refs = [torch.nn.Parameter(p.detach().float().clone()) for p in params]
+    kw = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ours, theirs = FusedAdamW(params, **kw), torch.optim.AdamW(refs, **kw)
+    for _ in range(3):
+        for p, q in zip(params, refs):
+            g = bf16(*p.shape)
+            p.grad, q.grad = g, g.float()
+        ours.step()
+        theirs.step()
+        for p, q in zip(params, refs):
+            assert (p.float() - q.detach()).abs().max().item() < 1e-2 * q.detach().abs().max().item()
+            q.data.copy_(p.float())  # the kernel rounds the parameter to bf16 each step
+    for p, q in zip(params, refs):
+        assert ours.state[p]["exp_avg"].dtype == torch.float32
+        assert rel_err(ours.state[p]["exp_avg"], theirs.state[q]["exp_avg"]) < 1e-4
+        assert rel_err(ours.state[p]["exp_avg_sq"], theirs.state[q]["exp_avg_sq"]) < 1e-4
+
+
 def test_diloco_fused_outer_step_matches_sgd():
     from torchft_b200.local_sgd import _FlatBuckets
     from torchft_b200.ops.outer_step import FusedOuterStep

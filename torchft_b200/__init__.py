@@ -15,6 +15,7 @@ _EXPORTS = {
     "DistributedDataParallel": ("torchft_b200.ddp", "DistributedDataParallel"),
     "Manager": ("torchft_b200.manager", "Manager"),
     "Optimizer": ("torchft_b200.optim", "OptimizerWrapper"),
+    "FusedAdamW": ("torchft_b200.optim", "FusedAdamW"),
     "ProcessGroupBabyNCCL": ("torchft_b200.process_group", "ProcessGroupBabyNCCL"),
     "ProcessGroupGloo": ("torchft_b200.process_group", "ProcessGroupGloo"),
     # the NVLink backend pulls in the CUDA kernel library
