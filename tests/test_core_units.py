@@ -353,3 +353,43 @@ def test_fused_adamw_matches_torch_and_keeps_its_state_tensors():
     assert torch.equal(ours[0], before)
     with pytest.raises(ValueError):
         FusedAdamW(ours, lr=-1.0)
+
+
+def test_peer_mappings_are_shared_and_closed_with_the_last_user(monkeypatch):
+    """``_PeerMappings`` opens a peer's heap once per process however many users map it and closes it when the
+    last one lets go (the peer's GPU memory stays allocated for as long as a mapping exists).  The CUDA-IPC
+    calls are replaced by a fake here."""
+    import contextlib
+    import ctypes
+
+    from torchft_b200.parallel import nvlink
+
+    calls = []
+
+    class FakeLib:
+        @staticmethod
+        def tft_p2p_peer_open(handle, out):
+            calls.append(("open", bytes(handle)))
+            ctypes.cast(out, ctypes.POINTER(ctypes.c_void_p))[0] = 0x1000 * len(calls)
+            return 0
+
+        @staticmethod
+        def tft_p2p_peer_close(ptr):
+            calls.append(("close", ptr.value))
+            return 0
+
+    monkeypatch.setattr(nvlink, "_lib_p2p", lambda: FakeLib)
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    monkeypatch.setattr(nvlink._PeerMappings, "_table", {})
+    dev = torch.device("cuda", 0)
+    a = nvlink._PeerMappings.acquire(b"peer-a", dev)
+    assert nvlink._PeerMappings.acquire(b"peer-a", dev) == a  # second user: same mapping, no second open
+    b = nvlink._PeerMappings.acquire(b"peer-b", dev)
+    assert a != b and nvlink._PeerMappings.open_count() == 2 and [c[0] for c in calls] == ["open", "open"]
+    nvlink._PeerMappings.release(b"peer-a", dev)
+    assert nvlink._PeerMappings.open_count() == 2  # one user of peer-a is left
+    nvlink._PeerMappings.release(b"peer-a", dev)
+    assert nvlink._PeerMappings.open_count() == 1 and calls[-1] == ("close", a)
+    nvlink._PeerMappings.release(b"peer-a", dev)  # unknown handle: nothing to do
+    nvlink._PeerMappings.release(b"peer-b", dev)
+    assert nvlink._PeerMappings.open_count() == 0 and calls[-1] == ("close", b)
