@@ -90,6 +90,8 @@ def case_attention():
            timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="smem")), flops=2.5 * fl)
     report("attention backward, dQ kernel with dS in tensor memory, dK/dV through shared memory",
            timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="tmem-dq")), flops=2.5 * fl)
+    report("attention backward, dQ kernel with dS in tensor memory, dK/dV with separate S and dP pipelines",
+           timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="split")), flops=2.5 * fl)
     report("attention backward (delta + dkdv + dq), P and dS in tensor memory",
            timeit(lambda: attention_bwd(do, q, k, v, o, lse, impl="tmem")), flops=2.5 * fl)
     # The library kernel the reference arm of bench.py runs: F.scaled_dot_product_attention (whatever

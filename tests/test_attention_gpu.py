@@ -112,7 +112,7 @@ def test_backward_kernels_agree_with_fp32(shape):
     do = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16)
     o, lse = attention_fwd(q, k, v)
     _, _, rq, rk, rv = reference(q, k, v, do)
-    for impl in ("smem", "tmem-dq", "tmem"):
+    for impl in ("smem", "tmem-dq", "split", "tmem"):
         dq, dk, dv = attention_bwd(do, q, k, v, o, lse, impl=impl)
         for name, got, want in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
             assert rel(got, want) < 2e-2 and norm_rel(got, want) < 8e-3, (impl, name, rel(got, want), norm_rel(got, want))

@@ -46,8 +46,8 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Opti
     return o, lse
 
 
-BWD_IMPL = os.environ.get("TFT_ATTN_BWD", "tmem-dq")
-assert BWD_IMPL in ("smem", "tmem", "tmem-dq"), f"TFT_ATTN_BWD must be 'smem', 'tmem' or 'tmem-dq', not {BWD_IMPL!r}"
+BWD_IMPL = os.environ.get("TFT_ATTN_BWD", "split")
+assert BWD_IMPL in ("smem", "tmem", "tmem-dq", "split"), f"TFT_ATTN_BWD must be 'smem', 'tmem', 'tmem-dq' or 'split', not {BWD_IMPL!r}"
 
 
 def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
@@ -57,7 +57,9 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
     """Gradients ``(dq, dk, dv)``; ``out`` may name preallocated (possibly strided) destinations.
 
     ``impl="smem"``: P and dS go through shared memory (``attention_bwd.cu``); ``"tmem"``: they stay in
-    tensor memory as MMA operands (``attention_bwd_tmem.cu``).  Default from ``TFT_ATTN_BWD``."""
+    tensor memory as MMA operands (``attention_bwd_tmem.cu``); ``"tmem-dq"``: the dQ kernel of the latter behind
+    the dK/dV kernel of the former; ``"split"``: the same with the dK/dV kernel whose S and dP products run as
+    separate pipelines.  Default from ``TFT_ATTN_BWD``."""
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
@@ -77,8 +79,9 @@ def attention_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
     which = impl or BWD_IMPL
     if which == "tmem":
         _lib.check(_lib.lib().tft_attn_bwd_tmem(*common, 7), "tft_attn_bwd_tmem")
-    elif which == "tmem-dq":  # dQ from tensor memory behind the shared-memory dK/dV kernel
-        _lib.check(_lib.lib().tft_attn_bwd_parts(*common, 3), "tft_attn_bwd_parts")
+    elif which in ("tmem-dq", "split"):  # dQ from tensor memory behind a shared-memory dK/dV kernel
+        # "split": the dK/dV kernel whose S and dP products run as separate pipelines
+        _lib.check(_lib.lib().tft_attn_bwd_parts(*common, 11 if which == "split" else 3), "tft_attn_bwd_parts")
         _lib.check(_lib.lib().tft_attn_bwd_tmem(*common, 4), "tft_attn_bwd_tmem")
     else:
         _lib.check(_lib.lib().tft_attn_bwd(*common), "tft_attn_bwd")
