@@ -87,12 +87,21 @@ class FusedAdamW(Optimizer):
             raise ValueError(f"invalid hyper-parameters: lr={lr} betas={betas} eps={eps} weight_decay={weight_decay}")
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         for group in self.param_groups:
-            group.setdefault("step", 0)
-            for p in group["params"]:
+            self._prepare(group)
+
+    def _prepare(self, group: Dict[str, Any]) -> None:
+        group.setdefault("step", 0)
+        for p in group["params"]:
+            if p not in self.state:
                 self.state[p] = {
                     "exp_avg": torch.zeros(p.shape, dtype=torch.float32, device=p.device),
                     "exp_avg_sq": torch.zeros(p.shape, dtype=torch.float32, device=p.device),
                 }
+
+    def add_param_group(self, param_group: Dict[str, Any]) -> None:
+        super().add_param_group(param_group)
+        if hasattr(self, "state"):  # the base constructor adds the initial groups before `state` is usable here
+            self._prepare(self.param_groups[-1])
 
     @torch.no_grad()
     def step(self, closure: Optional[object] = None) -> None:  # type: ignore[override]
