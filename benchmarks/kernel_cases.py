@@ -108,6 +108,19 @@ def case_attention():
            flops=2.5 * fl)
 
 
+def case_attention_default():
+    """Only the default forward and backward kernels, a few launches each: the case for a profiler capture."""
+    from torchft_b200.ops.attention import attention_bwd, attention_fwd
+
+    B, S, Hq, Hkv, D = 1, 4096, 32, 8, 128
+    q, k, v, do = bf16(B, S, Hq, D), bf16(B, S, Hkv, D), bf16(B, S, Hkv, D), bf16(B, S, Hq, D)
+    fl = 4.0 * S * S * D * Hq / 2
+    o, lse = attention_fwd(q, k, v)
+    report("attention forward (default kernel)", timeit(lambda: attention_fwd(q, k, v), iters=3, warmup=2), flops=fl)
+    report("attention backward (default kernels)", timeit(lambda: attention_bwd(do, q, k, v, o, lse), iters=3, warmup=2),
+           flops=2.5 * fl)
+
+
 def case_adamw():
     from torchft_b200.ops.functional import adamw_step_
 
@@ -144,7 +157,7 @@ def case_xent():
 
 
 if __name__ == "__main__":
-    cases = {"gemm": case_gemm, "attention": case_attention, "adamw": case_adamw, "norm": case_norm, "xent": case_xent}
+    cases = {"gemm": case_gemm, "attention": case_attention, "attention_default": case_attention_default, "adamw": case_adamw, "norm": case_norm, "xent": case_xent}
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     print(json.dumps({"peaks": PEAKS["source"], "hbm_gbs": PEAKS["hbm_gbs"], "bf16_tflops": PEAKS["bf16_tflops"]}))
     cases[which]()
