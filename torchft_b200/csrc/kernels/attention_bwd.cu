@@ -273,7 +273,7 @@ attn_dkdv_split_kernel(const __grid_constant__ CUtensorMap tq, const __grid_cons
   const int n_items = G * per_head;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_DKS_BARS; ++i) mbar_init(bar(i), (i == KS_P_READY || i == KS_DS_READY) ? 256 : 1);
+    for (int i = 0; i < NUM_DKS_BARS; ++i) mbar_init(bar(i), (i == KS_P_READY || i == KS_DS_READY) ? 8 : 1);  // one arrival per softmax warp
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq);
@@ -371,25 +371,18 @@ attn_dkdv_split_kernel(const __grid_constant__ CUtensorMap tq, const __grid_cons
     const int r = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     bool ok = true;
-    float next_lse = 0.f, next_dl = 0.f;
+    // Item t is query tile `it` of query head kv_head * G + hh; the row statistics of an item are
+    // fetched, and its indices advanced, one item ahead, in the shadow of the wait for the dV product.
+    int it = jt, hh = 0;
+    float lse = 0.f, dl = 0.f;
     if (n_items > 0) {
       const int row0 = jt * BLK + r;
       const long long stat0 = (static_cast<long long>(batch) * Hq + kv_head * G) * S + row0;
-      next_lse = row0 < S ? LSE[stat0] : 0.f;
-      next_dl = row0 < S ? delta[stat0] : 0.f;
+      lse = row0 < S ? LSE[stat0] : 0.f;
+      dl = row0 < S ? delta[stat0] : 0.f;
     }
     for (int t = 0; t < n_items; ++t) {
-      const int it = jt + t % per_head;
-      const int row = it * BLK + r;
-      const bool row_ok = row < S;
-      const float lse = next_lse, dl = next_dl;
-      if (t + 1 < n_items) {  // statistics of the next item travel while this one is processed
-        const int nhead = kv_head * G + (t + 1) / per_head;
-        const int nrow = (jt + (t + 1) % per_head) * BLK + r;
-        const long long nstat = (static_cast<long long>(batch) * Hq + nhead) * S + nrow;
-        next_lse = nrow < S ? LSE[nstat] : 0.f;
-        next_dl = nrow < S ? delta[nstat] : 0.f;
-      }
+      const bool row_ok = it * BLK + r < S;
       if (!mbar_wait(bar(KS_S_FULL), t & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = (it == jt);
@@ -420,7 +413,8 @@ attn_dkdv_split_kernel(const __grid_constant__ CUtensorMap tq, const __grid_cons
       for (int cc = 0; cc < 2; ++cc) store_row_chunk(smem + L::PDS, r, half * 2 + cc, p[cc]);
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(bar(KS_P_READY));
+      __syncwarp();  // the lanes' stores and fences are ordered before the one arrival of the warp
+      if (lane == 0) mbar_arrive(bar(KS_P_READY));
       // dP arrives behind the gradient products of the previous item; dS = P (dP - delta)
       if (!mbar_wait(bar(KS_DP_FULL), t & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -434,13 +428,31 @@ attn_dkdv_split_kernel(const __grid_constant__ CUtensorMap tq, const __grid_cons
 #pragma unroll
           for (int i = 0; i < 32; ++i) p[cc][i] *= (__uint_as_float(dv[cc][i]) - dl);
       }
+      // the next item's place and statistics, before the wait below so that the loads travel under it
+      int n_it = it + 1, n_hh = hh;
+      if (n_it == n_tiles) {
+        n_it = jt;
+        ++n_hh;
+      }
+      float n_lse = 0.f, n_dl = 0.f;
+      if (t + 1 < n_items) {
+        const int nrow = n_it * BLK + r;
+        const long long nstat = (static_cast<long long>(batch) * Hq + kv_head * G + n_hh) * S + nrow;
+        n_lse = nrow < S ? LSE[nstat] : 0.f;
+        n_dl = nrow < S ? delta[nstat] : 0.f;
+      }
       // ... and dS may replace P once the dV MMAs have read it
       if (!mbar_wait(bar(KS_P_FREE), t & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) store_row_chunk(smem + L::PDS, r, half * 2 + cc, p[cc]);
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(bar(KS_DS_READY));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(KS_DS_READY));
+      it = n_it;
+      hh = n_hh;
+      lse = n_lse;
+      dl = n_dl;
     }
     if (ok && mbar_wait(bar(KS_ACC_DONE), 0, abort_flag)) {
       tc_fence_after();
