@@ -19,7 +19,6 @@ replicated AdamW state (about 100 GB) fits one 180 GB GPU.  The JSON line names 
 from __future__ import annotations
 
 import json
-import math
 import os
 import socket
 import sys

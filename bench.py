@@ -193,7 +193,7 @@ def run_ours(args: argparse.Namespace) -> None:
     from torchft_b200.parallel.hsdp import HSDPEngine
     from torchft_b200.parallel.nvlink import NVLinkCommunicator, NVLinkShardComm, ProcessGroupNVLink, SymmetricHeap
     from torchft_b200.parallel.nvlink_heal import NVLinkCheckpointTransport
-    from torch.distributed import PrefixStore, TCPStore
+    from torch.distributed import TCPStore
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -13,7 +13,6 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 from torch import nn, optim
-from torch.distributed import ReduceOp
 
 from torchft_b200.local_sgd import DiLoCo, LocalSGD
 from torchft_b200.manager import Manager

@@ -5,7 +5,7 @@ errors at queue and wait time, spares, allow_heal=False, wrap_future, numerics.
 """
 
 from datetime import timedelta
-from unittest.mock import MagicMock, create_autospec, patch
+from unittest.mock import MagicMock, patch
 
 import pytest
 import torch

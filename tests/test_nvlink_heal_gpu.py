@@ -1,6 +1,5 @@
 """NVLink checkpoint transport: manifest + peer-memory pull, gate and lease semantics."""
 
-import threading
 import time
 import urllib.error
 from datetime import timedelta

@@ -1,6 +1,5 @@
 """Numerics of the sm_100a kernels against plain fp32 PyTorch references of the same ops."""
 
-import math
 
 import pytest
 import torch

@@ -3,7 +3,6 @@ collective of the torchft contract against each backend, as the reference's
 process_group_test.py does."""
 
 import gc
-import threading
 from concurrent.futures import ThreadPoolExecutor
 from datetime import timedelta
 from unittest.mock import MagicMock, create_autospec
