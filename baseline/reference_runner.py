@@ -91,7 +91,6 @@ def _run(args) -> None:
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus
     assert torch.cuda.device_count() == 1, "CUDA was initialised before the visible-device list was narrowed"
     torch.cuda.set_device(0)
@@ -245,7 +244,7 @@ def _run(args) -> None:
     sync_all()
     start.record()
     for _ in range(args.steps):
-        last = one_step(False)
+        one_step(False)
     end.record()
     sync_all()
     device_ms = start.elapsed_time(end)

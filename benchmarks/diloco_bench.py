@@ -115,7 +115,7 @@ def run_arm(arm: str, args, rank: int, world: int, heap) -> dict:
 
     algo.sync = timed_sync  # type: ignore[method-assign]
     with algo:
-        for s in range(args.syncs):
+        for _ in range(args.syncs):
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             for _ in range(args.sync_every):

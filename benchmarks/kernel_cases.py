@@ -136,7 +136,7 @@ def case_norm():
 
     rows, dim = 16384, 4096
     x, r, w, dy = bf16(rows, dim), bf16(rows, dim), bf16(dim), bf16(rows, dim)
-    y, h, rstd = rmsnorm_fwd(x, w, 1e-5, r)
+    _, h, rstd = rmsnorm_fwd(x, w, 1e-5, r)
     report("rmsnorm_fwd_kernel (+residual)", timeit(lambda: rmsnorm_fwd(x, w, 1e-5, r)), bytes_=rows * dim * 2 * 4)
     report("rmsnorm_bwd_kernel (+residual grad)", timeit(lambda: rmsnorm_bwd(dy, h, w, rstd, dy)), bytes_=rows * dim * 2 * 4)
 

@@ -250,7 +250,6 @@ class _Generic(grpc.GenericRpcHandler):
 
         table = {"/torchft.LighthouseService/Heartbeat": heartbeat, "/torchft.ManagerService/ShouldCommit": should_commit}
         if method == "/torchft.ManagerService/CheckpointMetadata":
-            rank = None
             return grpc.unary_unary_rpc_method_handler(
                 lambda request, context: (slow if S.CheckpointMetadataRequest.FromString(request).rank == 9 else big)(request, context))
         if method in table:

@@ -66,11 +66,9 @@ def _collectives(rank, world, port):
     heap = SymmetricHeap.get(256 << 20)
     comm = NVLinkCommunicator(heap, timeout=timedelta(seconds=20))
     comm.configure(store, rank, world, "epoch-a")
-    out = {}
     for dtype in (torch.bfloat16, torch.float32):
         for n in (8, 1000 * 8, (1 << 20) + 8 * 3):
             t = heap.alloc(n, dtype)
-            g = torch.Generator(device="cuda").manual_seed(1234 + rank)
             vals = [torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1234 + r)) for r in range(world)]
             t.copy_(vals[rank].to(dtype))
             comm.allreduce_(t, 1.0 / world)

@@ -295,7 +295,7 @@ def test_diloco_fused_outer_step_matches_sgd():
     comm = _FlatBuckets(params, None, False)
     fused = FusedOuterStep.maybe_create(params, backup, comm, outer)
     assert fused is not None
-    for it in range(3):
+    for _ in range(3):
         global_ref = [p.detach().clone() for p in ref_params]
         deltas = [torch.randn_like(p).mul(0.01).to(torch.bfloat16) for p in params]
         with torch.no_grad():
