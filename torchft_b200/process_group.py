@@ -49,17 +49,21 @@ if TYPE_CHECKING:
 logger: logging.Logger = logging.getLogger(__name__)
 
 
-def _get(q: "mp.Queue", timeout: Union[float, timedelta]) -> object:
-    """``q.get`` with a deadline; exceptions sent through the queue are raised here."""
-    if isinstance(timeout, timedelta):
-        timeout = timeout.total_seconds()
+def _take_reply(replies: "mp.Queue", budget: Union[float, timedelta]) -> object:
+    """Next message of a child process, within ``budget``.
+
+    A child reports a failure by sending the exception object itself; it is re-raised in the parent,
+    so the caller sees the child's error where it waited for the answer.  No message in time is a
+    ``TimeoutError`` (the usual sign of a wedged collective in the child).
+    """
+    seconds = budget.total_seconds() if isinstance(budget, timedelta) else float(budget)
     try:
-        v = q.get(timeout=timeout)
-    except queue.Empty as e:
-        raise TimeoutError(f"queue.get() timed out after {timeout} seconds") from e
-    if isinstance(v, Exception):
-        raise v
-    return v
+        message = replies.get(timeout=seconds)
+    except queue.Empty:
+        raise TimeoutError(f"no reply from the worker process within {seconds:g} s") from None
+    if isinstance(message, BaseException):
+        raise message
+    return message
 
 
 def create_store_client(store_addr: str) -> Store:
@@ -700,7 +704,7 @@ class ProcessGroupBaby(ProcessGroup):
         )
         self._event_thread.start()
         # surfaces start-up failures (store unreachable, rendezvous timeout, ...)
-        kind, _ = _get(self._reply_q, self._timeout)  # type: ignore[misc]
+        kind, _ = _take_reply(self._reply_q, self._timeout)  # type: ignore[misc]
         assert kind == "ready"
 
     def _event_loop(self, event_q: "mp.Queue") -> None:
@@ -735,7 +739,7 @@ class ProcessGroupBaby(ProcessGroup):
             self._cmd_q.put(req)
             if not expect_reply:
                 return None
-            kind, value = _get(self._reply_q, timeout if timeout is not None else self._timeout)  # type: ignore[misc]
+            kind, value = _take_reply(self._reply_q, timeout if timeout is not None else self._timeout)  # type: ignore[misc]
             return value
 
     def _run_func(self, name: str, *args: object, **kwargs: object) -> Work:
