@@ -29,27 +29,35 @@ from torchft_b200.process_group import ProcessGroupGloo
 
 
 class InjectedFailure(Exception):
-    pass
+    """Raised inside a rank's training loop to stand for the loss of that rank."""
 
 
 class FailureInjector:
+    """A plan of one-shot failures, keyed by (rank, step); shared by the threads of a replica group.
+
+    ``fail_at`` adds a point to the plan; ``check`` is called by every rank at every step and raises once
+    when that rank reaches a planned step (the entry is consumed, so the restarted group passes the same
+    step unharmed).  ``count`` says how many failures fired.
+    """
+
     def __init__(self) -> None:
-        self._lock = threading.Lock()
-        self._failures: Set[Tuple[int, int]] = set()
+        self._guard = threading.Lock()
+        self._plan: Set[Tuple[int, int]] = set()
         self.count = 0
 
     def fail_at(self, rank: int, step: int) -> "FailureInjector":
-        with self._lock:
-            self._failures.add((rank, step))
+        with self._guard:
+            self._plan.add((rank, step))
         return self
 
     def check(self, rank: int, step: int) -> None:
-        with self._lock:
-            key = (rank, step)
-            if key in self._failures:
+        with self._guard:
+            due = (rank, step) in self._plan
+            if due:
+                self._plan.discard((rank, step))
                 self.count += 1
-                self._failures.remove(key)
-                raise InjectedFailure(f"injected failure rank={rank} step={step}")
+        if due:
+            raise InjectedFailure(f"injected failure rank={rank} step={step}")
 
 
 @dataclass
