@@ -393,3 +393,23 @@ def test_peer_mappings_are_shared_and_closed_with_the_last_user(monkeypatch):
     nvlink._PeerMappings.release(b"peer-a", dev)  # unknown handle: nothing to do
     nvlink._PeerMappings.release(b"peer-b", dev)
     assert nvlink._PeerMappings.open_count() == 0 and calls[-1] == ("close", b)
+
+
+def test_api_reference_pages_name_importable_modules():
+    """Every ``automodule`` of the Sphinx pages under ``docs/source`` can be imported (the docs job would fail otherwise)."""
+    import importlib
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pages = os.path.join(root, "docs", "source")
+    names = []
+    for page in sorted(os.listdir(pages)):
+        if page.endswith(".rst"):
+            with open(os.path.join(pages, page)) as f:
+                names += re.findall(r"^\.\. automodule:: (\S+)", f.read(), flags=re.M)
+    assert len(names) >= 20
+    for name in names:
+        importlib.import_module(name)
+    with open(os.path.join(pages, "index.rst")) as f:
+        listed = set(re.findall(r"^    (\w+)$", f.read(), flags=re.M))
+    assert listed == {p[:-4] for p in os.listdir(pages) if p.endswith(".rst")} - {"index"}
